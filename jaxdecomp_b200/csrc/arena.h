@@ -1,0 +1,52 @@
+// Peer-visible device memory and the host-mapped status block (see arena.cpp).
+#pragma once
+#include <cstddef>
+#include <string>
+#include <vector>
+
+#include "status.h"
+#include "tile_map.h"
+
+namespace jdb {
+
+class SymmetricArena {
+ public:
+  static constexpr size_t kFlagBytes = 4096;
+  SymmetricArena(size_t bytes, int world, int me);
+  ~SymmetricArena();
+  SymmetricArena(const SymmetricArena&) = delete;
+  SymmetricArena& operator=(const SymmetricArena&) = delete;
+
+  std::string export_handles() const;                         // opaque blob to all-gather
+  void open_peers(const std::vector<std::string>& handles);  // blobs of all ranks, indexed by rank
+  void close();
+
+  size_t bytes() const { return bytes_; }
+  int world() const { return world_; }
+  int me() const { return me_; }
+  void* data(int peer) const { return data_.at(peer); }
+  void* flags(int peer) const { return flags_.at(peer); }
+
+ private:
+  size_t bytes_;
+  int world_, me_;
+  bool opened_ = false, closed_ = false;
+  std::vector<void*> data_, flags_;
+};
+
+class HostStatus {
+ public:
+  HostStatus();
+  ~HostStatus();
+  HostStatus(const HostStatus&) = delete;
+  HostStatus& operator=(const HostStatus&) = delete;
+  StatusBlock* host() const { return host_; }
+  StatusBlock* device() const { return dev_; }
+  void clear();
+
+ private:
+  StatusBlock* host_ = nullptr;
+  StatusBlock* dev_ = nullptr;
+};
+
+}  // namespace jdb

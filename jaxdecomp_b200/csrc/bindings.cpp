@@ -1,0 +1,167 @@
+// pybind11 module `_jdb200`: Python-facing entry points of the native core.
+//
+// Counterpart of the reference's nanobind module (src/csrc/jaxdecomp.cc:550-623),
+// which exposes init/finalize, pencil geometry, workspace queries and the XLA
+// FFI targets.  Here the entry points take raw device addresses and a CUDA
+// stream handle (both as integers), so the module has no dependency on
+// PyTorch's C++ API.  Failures are raised as Python exceptions; nothing exits
+// the process.
+#include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+
+#include <cstring>
+#include <stdexcept>
+
+#include "launch.h"
+#include "runtime.h"
+#include "trace.h"
+
+namespace py = pybind11;
+using namespace jdb;
+
+static void* P(uintptr_t v) { return reinterpret_cast<void*>(v); }
+
+static void raise_on(int rc, const char* what) {
+  if (rc == JD_OK) return;
+  std::string msg = std::string(what) + ": " + status_name(rc);
+  const char* detail = last_error_message();
+  if (detail && *detail) msg += std::string(" (") + detail + ")";
+  if (rc == JD_ERR_INVALID_ARG) throw py::value_error(msg);
+  throw std::runtime_error(msg);
+}
+
+PYBIND11_MODULE(_jdb200, m) {
+  m.doc() = "native core of jaxdecomp_b200 (sm_100a)";
+  m.attr("MAX_PEERS") = JD_MAX_PEERS;
+  m.attr("COPY") = (int)JD_COPY;
+  m.attr("FFT_POW2") = (int)JD_FFT_POW2;
+  m.attr("FFT_BLUESTEIN") = (int)JD_FFT_BLUESTEIN;
+  m.attr("BUF_USER_IN") = (int)BUF_USER_IN;
+  m.attr("BUF_USER_OUT") = (int)BUF_USER_OUT;
+  m.attr("BUF_SLOT_A") = (int)BUF_SLOT_A;
+  m.attr("BUF_SLOT_B") = (int)BUF_SLOT_B;
+  m.def("status_name", [](int s) { return std::string(status_name(s)); });
+
+  py::class_<PassDesc>(m, "PassDesc")
+      .def(py::init([]() {
+        PassDesc d;
+        std::memset(&d, 0, sizeof(d));
+        d.scale = 1.0;
+        d.B = 1;
+        return d;
+      }))
+#define RW(f) .def_readwrite(#f, &PassDesc::f)
+      RW(is_c) RW(is_t) RW(is_o) RW(is_b) RW(os_c) RW(os_t) RW(os_o) RW(os_b) RW(out_base) RW(C) RW(Tn) RW(On) RW(B)
+      RW(Cl) RW(Tl) RW(Ol) RW(npeers) RW(fft_mode) RW(M) RW(inverse) RW(T) RW(Cc) RW(pitch) RW(elem_bytes)
+      RW(load_t_contig) RW(store_t_contig) RW(use_bulk) RW(mul_mode) RW(vec_in) RW(vec_out) RW(scale)
+#undef RW
+      .def_property("in_ptr", [](const PassDesc& d) { return (uintptr_t)d.in; },
+                    [](PassDesc& d, uintptr_t v) { d.in = P(v); })
+      .def_property("twiddle", [](const PassDesc& d) { return (uintptr_t)d.twiddle; },
+                    [](PassDesc& d, uintptr_t v) { d.twiddle = P(v); })
+      .def_property("chirp", [](const PassDesc& d) { return (uintptr_t)d.chirp; },
+                    [](PassDesc& d, uintptr_t v) { d.chirp = P(v); })
+      .def_property("bhat", [](const PassDesc& d) { return (uintptr_t)d.bhat; },
+                    [](PassDesc& d, uintptr_t v) { d.bhat = P(v); })
+      .def("set_out", [](PassDesc& d, int p, uintptr_t v) {
+        if (p < 0 || p >= JD_MAX_PEERS) throw py::index_error("peer index");
+        d.out[p] = P(v);
+      })
+      .def("get_out", [](const PassDesc& d, int p) { return (uintptr_t)d.out[p]; })
+      .def("copy", [](const PassDesc& d) { return d; });
+
+  m.def("validate_pass", [](const PassDesc& d) { return validate_pass(d); });
+  m.def("run_pass_host", [](const PassDesc& d) { raise_on(run_pass_host(d), "run_pass_host"); });
+  m.def("launch_pass", [](const PassDesc& d, uintptr_t stream, uintptr_t status) {
+    raise_on(launch_pass(d, P(stream), (StatusBlock*)P(status)), "launch_pass");
+  });
+  m.def("pass_threads", &pass_threads);
+  m.def("pass_smem_bytes", &pass_smem_bytes);
+  m.def("get_fft_tables", [](int C, int M, int elem_bytes, bool device) {
+    FftTables t = get_fft_tables(C, M, elem_bytes, device);
+    return py::make_tuple((uintptr_t)t.twiddle, (uintptr_t)t.chirp, (uintptr_t)t.bhat);
+  });
+  m.def("clear_fft_tables", &clear_fft_tables);
+
+  py::class_<PlanStep>(m, "PlanStep")
+      .def(py::init<>())
+      .def_readwrite("desc", &PlanStep::desc)
+      .def_readwrite("in_kind", &PlanStep::in_kind)
+      .def_readwrite("out_kind", &PlanStep::out_kind)
+      .def_readwrite("copy_only", &PlanStep::copy_only)
+      .def_readwrite("copy_bytes", &PlanStep::copy_bytes)
+      .def("set_group_ranks", [](PlanStep& s, const std::vector<int>& r) {
+        if (r.size() > JD_MAX_PEERS) throw py::value_error("too many peers");
+        for (size_t i = 0; i < r.size(); ++i) s.group_ranks[i] = r[i];
+      });
+
+  py::class_<Runtime>(m, "Runtime")
+      .def(py::init<int, int>(), py::arg("world"), py::arg("me"))
+      .def("create_arena", &Runtime::create_arena)
+      .def("export_handles", [](const Runtime& r) { return py::bytes(r.export_handles()); })
+      .def("open_peers", [](Runtime& r, const std::vector<py::bytes>& hs) {
+        std::vector<std::string> v;
+        for (const auto& h : hs) v.push_back((std::string)h);
+        r.open_peers(v);
+      })
+      .def("destroy_arena", &Runtime::destroy_arena)
+      .def("has_arena", &Runtime::has_arena)
+      .def("slot_bytes", &Runtime::slot_bytes)
+      .def("slot_ptr", [](const Runtime& r, int slot, int peer) { return (uintptr_t)r.slot_ptr(slot, peer); })
+      .def("flag_ptr", [](const Runtime& r, int peer) { return (uintptr_t)r.flag_ptr(peer); })
+      .def("find_plan", &Runtime::find_plan)
+      .def("add_plan", [](Runtime& r, const std::string& key, const std::vector<PlanStep>& steps, long long slot_bytes) {
+        Plan p;
+        p.steps = steps;
+        p.slot_bytes = slot_bytes;
+        return r.add_plan(key, std::move(p));
+      })
+      .def("plan_slot_bytes", [](const Runtime& r, int id) { return r.plan(id).slot_bytes; })
+      .def("plan_num_steps", [](const Runtime& r, int id) { return r.plan(id).steps.size(); })
+      .def("num_plans", &Runtime::num_plans)
+      .def("cache_hits", &Runtime::cache_hits)
+      .def("cache_misses", &Runtime::cache_misses)
+      .def("clear_plans", &Runtime::clear_plans)
+      .def("execute", [](Runtime& r, int id, uintptr_t in, uintptr_t out, uintptr_t stream) {
+        raise_on(r.execute(id, P(in), P(out), P(stream)), "execute");
+      })
+      .def("barrier", [](Runtime& r, uintptr_t stream) { raise_on(r.barrier(P(stream)), "barrier"); })
+      .def("barriers_issued", &Runtime::barriers_issued)
+      .def("launches", &Runtime::launches)
+      .def("read_status", [](const Runtime& r) {
+        StatusBlock s = r.read_status();
+        return py::make_tuple(s.code, s.peer, s.expected, s.seen, s.where);
+      })
+      .def("clear_status", &Runtime::clear_status)
+      .def("status_device_ptr", [](const Runtime& r) { return (uintptr_t)r.status_device(); })
+      .def("set_timeout_ms", &Runtime::set_timeout_ms)
+      .def("wait_only", [](Runtime& r, int n, uint32_t epoch, long long timeout_ms, uintptr_t stream) {
+        raise_on(launch_wait_only(r.flag_ptr(r.me()), n, epoch, timeout_ms * 1000000LL, P(stream), r.status_device()),
+                 "wait_only");
+      })
+      .def_property_readonly("world", &Runtime::world)
+      .def_property_readonly("me", &Runtime::me);
+
+  // ---- trace log / profiler ------------------------------------------------------------------------------
+  m.def("trace_enabled", [](const std::string& logger, int level) { return trace_enabled(logger.c_str(), (TraceLevel)level); });
+  m.def("trace_write", [](const std::string& logger, int level, const std::string& msg) {
+    if (trace_enabled(logger.c_str(), (TraceLevel)level)) trace_write(logger.c_str(), (TraceLevel)level, "%s", msg.c_str());
+  });
+  m.def("trace_flush", &trace_flush);
+  m.def("trace_set_rank", &trace_set_rank);
+  m.def("trace_reconfigure", &trace_reconfigure);
+  m.def("trace_stack", &trace_stack);
+  m.def("profiler_mode", []() { return (int)StepProfiler::instance().mode(); });
+  m.def("profiler_set_mode", [](int mode) { StepProfiler::instance().set_mode((StepProfiler::Mode)mode); });
+  m.def("profiler_start", [](const std::string& n, uintptr_t stream) { StepProfiler::instance().start(n, P(stream)); });
+  m.def("profiler_stop", [](uintptr_t stream) { StepProfiler::instance().stop(P(stream)); });
+  m.def("profiler_switch", [](const std::string& n, uintptr_t stream) { StepProfiler::instance().switch_to(n, P(stream)); });
+  m.def("profiler_csv", []() { return StepProfiler::instance().to_csv(); });
+  m.def("profiler_markdown", []() { return StepProfiler::instance().to_markdown(); });
+  m.def("profiler_reset", []() { StepProfiler::instance().reset(); });
+  m.def("profiler_report", []() {
+    py::list out;
+    for (const auto& r : StepProfiler::instance().report()) out.append(py::make_tuple(r.name, r.count, r.ms));
+    return out;
+  });
+}

@@ -1,0 +1,103 @@
+// CPU emulation of the tile pass: the same descriptor, the same index
+// arithmetic (tile_map.h), the same tile movement (tile_ops.h) and the same
+// butterflies (fft_core.h) as the CUDA kernel, executed one tile at a time.
+// It lets the planner, the peer addressing and the FFT numerics be tested on a
+// machine without a GPU, with the buffers of all emulated ranks living in one
+// process.  It is a test vehicle, not a product path.
+#include <cstring>
+#include <vector>
+
+#include "launch.h"
+#include "tile_ops.h"
+
+namespace jdb {
+
+template <typename E>
+static void fft_rows_host(const PassDesc& d, E* tile) {
+  if constexpr (elem_traits<E>::is_complex) {
+    int logM = 0;
+    while ((1 << logM) < d.M) ++logM;
+    const int upr = d.M >> 3;
+    const int units = d.T * upr;
+    std::vector<E> regs((size_t)units * 8);
+    const int ns = fft_num_stages(logM);
+    int Ls = 1;
+    for (int s = 0; s < ns; ++s) {
+      const int rl = fft_stage_radix_log(logM, s);
+      for (int u = 0; u < units; ++u) stage_read(tile + (long long)(u / upr) * d.pitch, d.M, u % upr, &regs[(size_t)u * 8]);
+      for (int u = 0; u < units; ++u)
+        stage_compute_write(tile + (long long)(u / upr) * d.pitch, d.M, u % upr, Ls, rl, (const E*)d.twiddle,
+                            &regs[(size_t)u * 8]);
+      Ls <<= rl;
+    }
+  }
+}
+
+template <typename E>
+static int run_pass_host_t(const PassDesc& d) {
+  const bool fft = d.fft_mode != JD_COPY;
+  const int tiles_t = (d.Tn + d.T - 1) / d.T;
+  const int tiles_c = fft ? 1 : (d.C + d.Cc - 1) / d.Cc;
+  std::vector<E> tile((size_t)d.T * d.pitch);
+  for (int b = 0; b < d.B; ++b)
+    for (int o = 0; o < d.On; ++o)
+      for (int tt = 0; tt < tiles_t; ++tt)
+        for (int cc = 0; cc < tiles_c; ++cc) {
+          const int t0 = tt * d.T, c0 = cc * d.Cc;
+          tile_load<E>(d, tile.data(), o, t0, c0, b, 0, 1);
+          if (fft) {
+            fft_rows_host<E>(d, tile.data());
+            if (d.fft_mode == JD_FFT_BLUESTEIN) {
+              bluestein_filter<E>(d, tile.data(), 0, 1);
+              fft_rows_host<E>(d, tile.data());
+            }
+          }
+          tile_store<E>(d, tile.data(), o, t0, c0, b, 0, 1);
+        }
+  return JD_OK;
+}
+
+int run_pass_host(const PassDesc& d) {
+  int rc = validate_pass(d);
+  if (rc != JD_OK) return rc;
+  if (d.fft_mode == JD_COPY) {
+    if (d.elem_bytes == 4) return run_pass_host_t<float>(d);
+    if (d.elem_bytes == 8) return run_pass_host_t<cx<float>>(d);
+    if (d.elem_bytes == 16) return run_pass_host_t<cx<double>>(d);
+    return JD_ERR_INVALID_ARG;
+  }
+  if (d.elem_bytes == 8) return run_pass_host_t<cx<float>>(d);
+  if (d.elem_bytes == 16) return run_pass_host_t<cx<double>>(d);
+  return JD_ERR_INVALID_ARG;
+}
+
+// Structural checks shared by the host emulation and the CUDA launcher.
+int validate_pass(const PassDesc& d) {
+  if (d.C < 1 || d.Tn < 1 || d.On < 1 || d.B < 1) return JD_ERR_INVALID_ARG;
+  if (d.Cl < 1 || d.Tl < 1 || d.Ol < 1) return JD_ERR_INVALID_ARG;
+  if (d.C % d.Cl || d.Tn % d.Tl || d.On % d.Ol) return JD_ERR_INVALID_ARG;
+  const int np = (d.C / d.Cl) + (d.Tn / d.Tl) + (d.On / d.Ol) - 2;
+  if (np != d.npeers || np < 1 || np > JD_MAX_PEERS) return JD_ERR_INVALID_ARG;
+  if (d.T < 1 || d.pitch < 1) return JD_ERR_INVALID_ARG;
+  if (d.elem_bytes != 4 && d.elem_bytes != 8 && d.elem_bytes != 16) return JD_ERR_INVALID_ARG;
+  if (d.load_t_contig ? d.is_t != 1 : d.is_c != 1) return JD_ERR_INVALID_ARG;
+  if (d.store_t_contig ? d.os_t != 1 : d.os_c != 1) return JD_ERR_INVALID_ARG;
+  if (d.fft_mode == JD_COPY) {
+    if (d.Cc < 1 || d.pitch < d.Cc) return JD_ERR_INVALID_ARG;
+  } else {
+    if (d.elem_bytes == 4) return JD_ERR_INVALID_ARG;
+    if (d.M < 8 || (d.M & (d.M - 1))) return JD_ERR_INVALID_ARG;
+    if (d.pitch < d.M || !d.twiddle) return JD_ERR_INVALID_ARG;
+    if (d.fft_mode == JD_FFT_POW2 && d.M != d.C) return JD_ERR_INVALID_ARG;
+    if (d.fft_mode == JD_FFT_BLUESTEIN && (d.M < 2 * d.C - 1 || !d.chirp || !d.bhat)) return JD_ERR_INVALID_ARG;
+  }
+  if (d.vec_in || d.vec_out) {
+    if (d.elem_bytes != 8 || (d.pitch & 1)) return JD_ERR_INVALID_ARG;
+  }
+  for (int p = 0; p < d.npeers; ++p)
+    if (!d.out[p]) return JD_ERR_INVALID_ARG;
+  if (!d.in) return JD_ERR_INVALID_ARG;
+  return JD_OK;
+}
+
+}  // namespace jdb

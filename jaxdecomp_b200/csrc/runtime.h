@@ -1,0 +1,107 @@
+// Process-wide runtime of the native backend: the peer-visible arena, the
+// status block, the FFT tables and the plan cache with its executor.
+//
+// Counterpart of the reference's GridDescriptorManager singleton, which caches
+// one executor per (gdims, pdims, precision, layout, backend) descriptor and
+// owns the cuDecomp handle and workspaces
+// (src/csrc/grid_descriptor_mgr.cc:15-144, include/grid_descriptor_mgr.h:20-67).
+// Here a cached plan is a list of tile passes with symbolic buffer bindings;
+// executing it is one call from Python that launches every pass and every
+// cross-rank barrier on the caller's stream.
+#pragma once
+#include <cstdint>
+#include <map>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "arena.h"
+#include "launch.h"
+
+namespace jdb {
+
+struct FftTables {
+  const void* twiddle = nullptr;
+  const void* chirp = nullptr;
+  const void* bhat = nullptr;
+};
+FftTables get_fft_tables(int C, int M, int elem_bytes, bool device);
+void clear_fft_tables();
+
+enum BufferKind : int32_t {
+  BUF_USER_IN = 0,   // the operand passed to execute()
+  BUF_USER_OUT = 1,  // the result tensor passed to execute()
+  BUF_SLOT_A = 2,    // arena slot 0 (peer visible)
+  BUF_SLOT_B = 3,    // arena slot 1 (peer visible)
+};
+
+struct PlanStep {
+  PassDesc desc;               // pointers of in/out are filled in at execution time
+  int32_t in_kind = BUF_USER_IN;
+  int32_t out_kind = BUF_USER_OUT;
+  int32_t copy_only = 0;       // 1: plain device-to-device copy of copy_bytes from in to out
+  long long copy_bytes = 0;
+  int32_t group_ranks[JD_MAX_PEERS] = {0};  // arena rank of destination peer p (npeers entries)
+};
+
+struct Plan {
+  std::vector<PlanStep> steps;
+  long long slot_bytes = 0;  // bytes each arena slot must provide
+  long long hits = 0;
+};
+
+class Runtime {
+ public:
+  Runtime(int world, int me);
+  ~Runtime();
+
+  // arena life cycle (collective: every rank calls with the same sizes)
+  void create_arena(size_t slot_bytes);
+  std::string export_handles() const;
+  void open_peers(const std::vector<std::string>& handles);
+  void destroy_arena();
+  size_t slot_bytes() const { return slot_bytes_; }
+  bool has_arena() const { return (bool)arena_; }
+  void* slot_ptr(int slot, int peer) const;
+  uint32_t* flag_ptr(int peer) const;
+
+  // plan cache
+  int find_plan(const std::string& key);  // -1 if absent; counts a hit otherwise
+  int add_plan(const std::string& key, Plan plan);
+  const Plan& plan(int id) const { return plans_.at(id); }
+  size_t num_plans() const { return plans_.size(); }
+  long long cache_hits() const { return hits_; }
+  long long cache_misses() const { return misses_; }
+  void clear_plans();
+
+  // execution
+  int execute(int plan_id, const void* in, void* out, void* stream);
+  int barrier(void* stream);
+  long long barriers_issued() const { return host_epoch_; }
+  long long launches() const { return launches_; }
+
+  // status
+  StatusBlock read_status() const;
+  void clear_status();
+  StatusBlock* status_device() const { return status_ ? status_->device() : nullptr; }
+
+  void set_timeout_ms(long long ms) { timeout_ns_ = ms * 1000000LL; }
+  int world() const { return world_; }
+  int me() const { return me_; }
+
+ private:
+  int world_, me_;
+  std::unique_ptr<SymmetricArena> arena_;
+  std::unique_ptr<HostStatus> status_;
+  size_t slot_bytes_ = 0;
+  long long timeout_ns_ = 2000000000LL;
+  // hazard tracking (identical on every rank because all ranks issue the same sequence)
+  long long host_epoch_ = 0;
+  long long slot_written_[2] = {-1, -1};  // epoch during which peers last wrote the slot
+  long long slot_read_[2] = {-1, -1};     // epoch during which this rank last read the slot
+  std::map<std::string, int> plan_index_;
+  std::vector<Plan> plans_;
+  long long hits_ = 0, misses_ = 0, launches_ = 0;
+};
+
+}  // namespace jdb

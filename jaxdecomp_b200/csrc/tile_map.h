@@ -1,0 +1,82 @@
+// Descriptor of one "tile pass" and the index arithmetic that maps an element
+// of a rank's local block to (destination peer, offset in that peer's buffer).
+//
+// A pass reads a local 3-D block (plus an optional batch dimension) through
+// arbitrary strides, optionally Fourier-transforms it along one axis, and
+// scatters the result into up to JD_MAX_PEERS destination buffers.  The three
+// local axes are given roles:
+//   c  the transform axis (or, in copy mode, the axis that is contiguous in the input),
+//   t  the axis that is tiled together with c (contiguous on the output side
+//      for a rotating pass, or on the input side for a strided transform),
+//   o  the remaining axis: one value per thread block.
+// A tiled all-to-all over P ranks that splits one of the axes is expressed by
+// that axis's chunk extent (Cl, Tl or Ol = extent / P): element index / chunk
+// selects the peer, index % chunk is the coordinate on the peer, and out_base
+// holds this rank's constant offset along the concatenation axis.  Local axis
+// permutations are folded into the output strides.  One descriptor therefore
+// covers every step group of the distributed FFT, the six pencil transposes in
+// both layout modes, and purely local passes (npeers == 1).
+//
+// This is the device-side counterpart of what the reference delegates to
+// cudecompTranspose* + cufftXtExec (src/csrc/fft.cu:460-535) or to XLA's
+// all_to_all + transpose (src/jaxdecomp/_src/jax/fft.py:94-135).
+//
+// The header is plain C++ so that the CPU emulation used by the unit tests
+// shares the exact arithmetic of the kernels.
+#pragma once
+#include <cstdint>
+
+#if defined(__CUDACC__)
+#define JD_HD __host__ __device__ __forceinline__
+#else
+#define JD_HD inline
+#endif
+
+#define JD_MAX_PEERS 16
+
+namespace jdb {
+
+enum FftMode : int32_t { JD_COPY = 0, JD_FFT_POW2 = 1, JD_FFT_BLUESTEIN = 2 };
+
+struct PassDesc {
+  // strides in elements
+  long long is_c, is_t, is_o, is_b;
+  long long os_c, os_t, os_o, os_b;
+  long long out_base;
+  int32_t C, Tn, On, B;   // extents of c, t, o and batch
+  int32_t Cl, Tl, Ol;     // per-peer chunk extents (== full extent when the axis is not split)
+  int32_t npeers;
+  int32_t fft_mode;       // FftMode
+  int32_t M;              // transform length held in shared memory (C, or the Bluestein length)
+  int32_t inverse;        // 1: conjugate (inverse-direction) transform
+  int32_t T, Cc;          // tile extents along t and c (Cc == M-row in fft modes)
+  int32_t pitch;          // shared-memory row pitch in elements
+  int32_t elem_bytes;     // 4, 8 or 16
+  int32_t load_t_contig;  // 1: input is contiguous along t (is_t == 1), else along c
+  int32_t store_t_contig; // 1: output is contiguous along t (os_t == 1), else along c
+  int32_t use_bulk;       // 1: fetch rows with bulk async copies (needs 16-byte aligned rows)
+  int32_t mul_mode;       // 0 none; 1 multiply the result by mul[] (same indexing as the output of peer 0)
+  int32_t vec_in;         // 1: 8-byte elements may be loaded two at a time (16-byte accesses)
+  int32_t vec_out;        // 1: 8-byte elements may be stored two at a time
+  double scale;
+  const void* in;
+  void* out[JD_MAX_PEERS];
+  const void* twiddle;    // M entries: exp(-2*pi*i*n/M)
+  const void* chirp;      // Bluestein: C entries exp(-i*pi*n^2/C)
+  const void* bhat;       // Bluestein: M entries FFT_M(conj chirp, wrapped) / M
+  const void* mul;        // optional pointwise multiplier
+};
+
+// (c, t, o, b) of the local block -> destination peer and element offset there.
+JD_HD void out_location(const PassDesc& d, int c, int t, int o, int b, int& peer, long long& off) {
+  const int pc = c / d.Cl, pt = t / d.Tl, po = o / d.Ol;
+  peer = pc + pt + po;
+  off = d.out_base + (long long)(c - pc * d.Cl) * d.os_c + (long long)(t - pt * d.Tl) * d.os_t +
+        (long long)(o - po * d.Ol) * d.os_o + (long long)b * d.os_b;
+}
+
+JD_HD long long in_location(const PassDesc& d, int c, int t, int o, int b) {
+  return (long long)c * d.is_c + (long long)t * d.is_t + (long long)o * d.is_o + (long long)b * d.is_b;
+}
+
+}  // namespace jdb

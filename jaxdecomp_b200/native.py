@@ -1,0 +1,176 @@
+"""Build and load the native core (``_jdb200``: CUDA kernels for sm_100a plus
+the C++ runtime around them).
+
+The shared object is built in-tree, next to this file, with explicit ``nvcc``
+commands (``-gencode arch=compute_100a,code=sm_100a``), so that it travels with
+the source tree to machines that have a GPU.  A content hash of the sources is
+stored beside it; the library is rebuilt only when the sources changed.  The
+reference builds its native module with CMake/scikit-build against cuDecomp
+(``CMakeLists.txt:1-123``); this build has no third-party dependency besides
+the CUDA toolkit and pybind11.
+"""
+from __future__ import annotations
+
+import fcntl
+import hashlib
+import importlib.util
+import os
+import shutil
+import subprocess
+import sys
+import sysconfig
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+from typing import Optional
+
+from .utils.errors import NativeExtensionError
+
+_HERE = Path(__file__).resolve().parent
+_CSRC = _HERE / "csrc"
+_SO = _HERE / ("_jdb200" + (sysconfig.get_config_var("EXT_SUFFIX") or ".so"))
+_HASH = _HERE / "_jdb200.hash"
+_OBJ = _CSRC / "build"
+
+SOURCES = [
+    "bindings.cpp",
+    "runtime.cpp",
+    "arena.cpp",
+    "tables.cpp",
+    "trace.cpp",
+    "cpu_ref.cpp",
+    "fft_pass.cu",
+    "signal.cu",
+    "halo.cu",
+    "cic.cu",
+    "kspace.cu",
+]
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-lineinfo", "-O3", "-std=c++17",
+    "--expt-relaxed-constexpr",
+    "-Xcompiler", "-fPIC",
+    "-Xcompiler", "-fvisibility=hidden",
+]
+
+_module = None
+_load_error: Optional[str] = None
+
+
+def _nvcc() -> Optional[str]:
+    cand = os.environ.get("NVCC") or shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    return cand if cand and os.path.exists(cand) else None
+
+
+def _existing_sources():
+    return [s for s in SOURCES if (_CSRC / s).exists()]
+
+
+def _source_hash() -> str:
+    h = hashlib.sha256()
+    files = sorted(p for p in _CSRC.iterdir() if p.suffix in (".cu", ".cpp", ".h", ".cuh"))
+    for p in files:
+        h.update(p.name.encode())
+        h.update(p.read_bytes())
+    h.update(" ".join(NVCC_FLAGS).encode())
+    return h.hexdigest()
+
+
+def is_built() -> bool:
+    return _SO.exists() and _HASH.exists() and _HASH.read_text().strip() == _source_hash()
+
+
+def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False) -> Path:
+    """Compile every source for sm_100a and link ``_jdb200``.  Safe to call from
+    several processes at once (file lock); a no-op when the library is current."""
+    nvcc = _nvcc()
+    if nvcc is None:
+        raise NativeExtensionError("nvcc not found; cannot build the native core")
+    _OBJ.mkdir(parents=True, exist_ok=True)
+    lock_path = _OBJ / ".lock"
+    with open(lock_path, "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if is_built() and not force:
+                return _SO
+            import pybind11
+
+            inc = ["-I", sysconfig.get_paths()["include"], "-I", pybind11.get_include(), "-I", str(_CSRC)]
+            flags = list(NVCC_FLAGS)
+            if ptxas_info:
+                flags += ["-Xptxas", "-v"]
+
+            def compile_one(src: str):
+                obj = _OBJ / (src + ".o")
+                cmd = [nvcc, *flags, *inc, "-c", str(_CSRC / src), "-o", str(obj)]
+                r = subprocess.run(cmd, capture_output=True, text=True)
+                if r.returncode != 0:
+                    raise NativeExtensionError(f"nvcc failed for {src}:\n{r.stdout}\n{r.stderr}")
+                if verbose or ptxas_info:
+                    sys.stderr.write(r.stderr)
+                return obj
+
+            with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 2)) as ex:
+                objs = list(ex.map(compile_one, _existing_sources()))
+            tmp = _SO.with_suffix(".tmp")
+            cmd = [nvcc, "-shared", "-o", str(tmp), *[str(o) for o in objs], "-ldl", "-lpthread",
+                   "-gencode", "arch=compute_100a,code=sm_100a"]
+            r = subprocess.run(cmd, capture_output=True, text=True)
+            if r.returncode != 0:
+                raise NativeExtensionError(f"link failed:\n{r.stdout}\n{r.stderr}")
+            os.replace(tmp, _SO)
+            _HASH.write_text(_source_hash())
+            return _SO
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+
+
+def load(build_if_needed: bool = True):
+    """Import the native module, building it first if it is missing or stale."""
+    global _module, _load_error
+    if _module is not None:
+        return _module
+    try:
+        if not is_built():
+            if not build_if_needed:
+                raise NativeExtensionError("native core is not built; run `python -m jaxdecomp_b200.native`")
+            build()
+        spec = importlib.util.spec_from_file_location("jaxdecomp_b200._jdb200", str(_SO))
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        sys.modules["jaxdecomp_b200._jdb200"] = mod
+        _module = mod
+        return mod
+    except Exception as e:  # noqa: BLE001
+        _load_error = f"{type(e).__name__}: {e}"
+        raise
+
+
+def available() -> bool:
+    """True when the native module can be imported (it also works, for the CPU
+    emulation and the host-side utilities, on a machine without a GPU)."""
+    try:
+        load()
+        return True
+    except Exception:  # noqa: BLE001
+        return False
+
+
+def require():
+    """Return the native module or raise a loud, explicit error."""
+    try:
+        return load()
+    except Exception as e:  # noqa: BLE001
+        raise NativeExtensionError(
+            "the native sm_100a core of jaxdecomp_b200 could not be built or loaded "
+            f"({_load_error or e}); refusing to fall back to library kernels on a CUDA tensor"
+        ) from e
+
+
+def so_path() -> Path:
+    return _SO
+
+
+if __name__ == "__main__":
+    p = build(verbose=True, force="--force" in sys.argv, ptxas_info="--ptxas" in sys.argv)
+    print(p)

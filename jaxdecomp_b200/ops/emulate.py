@@ -1,0 +1,87 @@
+"""Single-process CPU emulation of the native backend on a whole mesh.
+
+All ranks of a ``pdims`` mesh are emulated in one process: each holds its
+local block in host memory, and every compiled pass is executed for all ranks
+(one after the other) by the CPU implementation of the tile pass in the native
+module, which shares its index arithmetic and butterflies with the CUDA
+kernel.  Destination pointers of the emulated peers point into the other
+ranks' host buffers, so peer addressing, chunk routing and the fused
+permutations are exercised exactly as on NVLink -- without a GPU.  Used by the
+unit tests; not a product path.
+"""
+from __future__ import annotations
+
+from typing import List, Sequence
+
+import torch
+
+from . import passes as _passes
+from .plan import Step
+
+
+def _elem_bytes(dtype: torch.dtype) -> int:
+    return torch.empty((), dtype=dtype).element_size()
+
+
+def split_blocks(x: torch.Tensor, pdims: Sequence[int], spec_axes=(0, 1)) -> List[torch.Tensor]:
+    """Cut a global array into the row-major list of local blocks of an
+    X-pencil layout (array axis ``spec_axes[k]`` sharded by mesh axis ``k``)."""
+    p0, p1 = pdims
+    nb = x.dim() - 3
+    out = []
+    for i in range(p0):
+        for j in range(p1):
+            blk = x
+            for k, (p, c) in enumerate(((p0, i), (p1, j))):
+                ax = nb + spec_axes[k]
+                n = blk.shape[ax] // p
+                blk = blk.narrow(ax, c * n, n)
+            out.append(blk.contiguous())
+    return out
+
+
+def emulate_steps(blocks: List[torch.Tensor], steps: Sequence[Step], pdims: Sequence[int], inverse: bool = False,
+                  scale: float = 1.0) -> List[torch.Tensor]:
+    """Run a step list on the blocks of all ranks (row-major rank order) and
+    return the per-rank results."""
+    from .. import native as _native
+
+    nat = _native.require()
+    p0, p1 = int(pdims[0]), int(pdims[1])
+    world = p0 * p1
+    assert len(blocks) == world
+    dtype = blocks[0].dtype
+    eb = _elem_bytes(dtype)
+    nbatch = 1
+    if blocks[0].dim() == 4:
+        nbatch = blocks[0].shape[0]
+    compiled = []
+    for r in range(world):
+        coords = (r // p1, r % p1)
+        ps, final_shape = _passes.compile_passes(steps, blocks[r].shape[-3:], pdims, coords)
+        compiled.append(ps)
+    npass = len(compiled[0])
+    last_fft = max((i for i, p in enumerate(compiled[0]) if p.fft), default=-1)
+    cur = [b.contiguous() for b in blocks]
+    for i in range(npass):
+        shape_i = compiled[0][i].out_shape
+        full = ((nbatch,) if blocks[0].dim() == 4 else ()) + tuple(shape_i)
+        nxt = [torch.zeros(full, dtype=dtype) for _ in range(world)]
+        for r in range(world):
+            sp = compiled[r][i]
+            coords = (r // p1, r % p1)
+            d = _passes.fill_desc(nat, sp, eb, inverse, scale if i == last_fft else 1.0, nbatch,
+                                  remote=sp.npeers > 1, device_tables=False)
+            d.use_bulk = 0
+            d.in_ptr = cur[r].data_ptr()
+            for p in range(sp.npeers):
+                if sp.mesh_axis is None:
+                    dst = r
+                elif sp.mesh_axis == 0:
+                    dst = p * p1 + coords[1]
+                else:
+                    dst = coords[0] * p1 + p
+                d.set_out(p, nxt[dst].data_ptr())
+            nat.run_pass_host(d)
+        cur = nxt
+    return cur
