@@ -1,0 +1,305 @@
+#!/usr/bin/env python
+"""Headline benchmark: pfft3d + pifft3d round trip on a 1024^3 complex64 grid.
+
+    python bench.py --gpus 1 --steps 10 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29511 bench.py --gpus 8 --steps 10 --warmup 3
+
+One step = one forward and one inverse distributed FFT of the same global grid
+(strong scaling: the grid is fixed, ranks share it), the quantity the
+reference's benchmark alternates on one buffer (benchmarks/bench.py:68-70).
+Timing: CUDA events on the launching stream between barrier+synchronize pairs,
+maximum over ranks.  Rank 0 prints one JSON line.
+
+`--impl reference` would run the unmodified reference (JAX) from
+baseline/_ref; JAX is not installable offline on this image, so that arm
+reports itself unavailable.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+# published forward-only pfft3d times of the reference, 1024^3 complex64, H100 (ms), by GPU count
+PUBLISHED_FWD_MS = {2: 29.0, 4: 13.0, 8: 16.0}
+
+
+def reference_arm(args):
+    reason = None
+    try:
+        sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
+        import jax  # noqa: F401
+        import jaxdecomp  # noqa: F401
+    except Exception as e:  # noqa: BLE001
+        reason = (f"reference not installable offline: jax/jaxlib and nanobind are absent from the image and the wheelhouse "
+                  f"({type(e).__name__}: {e})")
+    if reason is None:
+        reason = "reference import succeeded unexpectedly but no runner is wired for it on this image"
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(json.dumps({"impl": "reference", "unavailable": reason}))
+    return 0
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs."""
+
+    def __init__(self, index: int, period: float = 0.2):
+        super().__init__(daemon=True)
+        self.index, self.period = index, period
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop_evt = threading.Event()
+        self.ok = False
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            uuid = None
+            try:
+                import torch
+
+                uuid = str(torch.cuda.get_device_properties(index).uuid)
+            except Exception:  # noqa: BLE001
+                pass
+            self.h = None
+            if uuid:
+                for cand in (uuid, "GPU-" + uuid):
+                    try:
+                        self.h = pynvml.nvmlDeviceGetHandleByUUID(cand.encode() if isinstance(cand, str) else cand)
+                        break
+                    except Exception:  # noqa: BLE001
+                        continue
+            if self.h is None:
+                self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:  # noqa: BLE001
+            self.ok = False
+
+    def run(self):
+        if not self.ok:
+            return
+        nv = self.nv
+        names = {
+            getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+        }
+        while not self._stop_evt.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:  # noqa: BLE001
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:  # noqa: BLE001
+                pass
+            self._stop_evt.wait(self.period)
+
+    def stop(self):
+        self._stop_evt.set()
+        if self.is_alive():
+            self.join(timeout=2.0)
+        return {
+            "sm_mhz": statistics.median(self.samples) if self.samples else None,
+            "sm_max_mhz": self.max_mhz,
+            "reasons": sorted(self.reasons),
+            "samples": len(self.samples),
+        }
+
+
+def pick_pdims(n: int, override: str | None):
+    if override:
+        a, b = override.lower().split("x")
+        return int(a), int(b)
+    env = os.environ.get("JD_BENCH_PDIMS")
+    if env:
+        a, b = env.lower().split("x")
+        return int(a), int(b)
+    # slab decomposition moves the least data over NVLink (one exchange per transform)
+    return (1, n)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "torch"])
+    ap.add_argument("--size", type=int, default=1024, help="grid points per side (headline: 1024)")
+    ap.add_argument("--dtype", default="c64", choices=["c64", "c128"])
+    ap.add_argument("--pdims", default=None, help="process grid as P0xP1 (default: slab 1xN)")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    import torch
+    import torch.distributed as dist
+
+    import jaxdecomp_b200 as jd
+    from jaxdecomp_b200.ops import b200_backend
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run for N > 1")
+    device = jd.init_distributed()
+    backend = "b200" if args.impl == "ours" else "torch"
+    warmup = max(3, args.warmup)
+    steps = max(1, args.steps)
+    n = args.size
+    dtype = torch.complex64 if args.dtype == "c64" else torch.complex128
+    pdims = pick_pdims(world, args.pdims)
+    mesh = jd.make_mesh(pdims, ("z", "y"))
+    p0, p1 = pdims
+    lshape = (n // p0, n // p1, n)
+    gen = torch.Generator(device=device).manual_seed(0 + rank)
+    real_dtype = torch.float32 if dtype == torch.complex64 else torch.float64
+    x0 = torch.complex(torch.randn(lshape, generator=gen, device=device, dtype=real_dtype),
+                       torch.randn(lshape, generator=gen, device=device, dtype=real_dtype))
+    x = jd.ShardedTensor(x0, mesh)
+
+    def sync_all():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step(v):
+        return jd.pifft3d(jd.pfft3d(v, backend=backend), backend=backend)
+
+    # correctness of the timed path (also the first warm-up): round trip returns the input
+    y = step(x)
+    err = float(((y.local - x0).abs().max() / x0.abs().max()).item())
+    if world > 1:
+        t = torch.tensor([err], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        err = float(t.item())
+    v = x
+    for _ in range(warmup):
+        v = step(v)
+    sync_all()
+    sampler = ClockSampler(device.index or 0)
+    sampler.start()
+    launches0 = b200_backend.launches(mesh) if backend == "b200" else 0
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync_all()
+    ev0.record()
+    for _ in range(steps):
+        v = step(v)
+    ev1.record()
+    sync_all()
+    ms = ev0.elapsed_time(ev1) / steps
+    launches = (b200_backend.launches(mesh) - launches0) if backend == "b200" else 0
+    clocks = sampler.stop()
+    t = torch.tensor([ms], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    if backend == "b200":
+        b200_backend.check_status(mesh, sync=True)
+
+    # ---- end-to-end: per step, H2D of the step's input from pinned memory and D2H of a result scalar ----
+    e2e = None
+    if not args.no_e2e:
+        del v, y
+        host = torch.empty(lshape, dtype=dtype, pin_memory=True)
+        host.copy_(x0)
+        bufs = [torch.empty_like(x0), x0]
+        copy_stream = torch.cuda.Stream()
+        main_stream = torch.cuda.current_stream()
+        ready = [torch.cuda.Event(), torch.cuda.Event()]
+        consumed = [torch.cuda.Event(), torch.cuda.Event()]
+
+        def prefetch(i):
+            with torch.cuda.stream(copy_stream):
+                copy_stream.wait_event(consumed[i])
+                bufs[i].copy_(host, non_blocking=True)
+                ready[i].record(copy_stream)
+
+        def e2e_steps(k):
+            consumed[0].record(main_stream)
+            consumed[1].record(main_stream)
+            prefetch(0)
+            acc = 0.0
+            for s in range(k):
+                i = s % 2
+                if s + 1 < k:
+                    prefetch(1 - i)
+                main_stream.wait_event(ready[i])
+                out = step(jd.ShardedTensor(bufs[i], mesh))
+                consumed[i].record(main_stream)
+                acc += float(out.local.real[0, 0, :8].sum().item())  # device -> host read of a result scalar
+            return acc
+
+        e2e_steps(2)
+        sync_all()
+        t0 = time.perf_counter()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        e2e_steps(steps)
+        e1.record()
+        sync_all()
+        e_ms = e0.elapsed_time(e1) / steps
+        t = torch.tensor([e_ms], device=device, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e_ms = float(t.item())
+        e2e = {"ms_per_step": e_ms, "wall_ms_per_step": (time.perf_counter() - t0) * 1e3 / steps,
+               "h2d_bytes_per_step": host.numel() * host.element_size() * world, "d2h_bytes_per_step": 4 * world}
+
+    total = float(n) ** 3
+    flops = 2 * 5.0 * total * math.log2(total)  # forward + inverse, 5 N log2 N each
+    gflops = flops / (ms * 1e-3) / 1e9
+    base = PUBLISHED_FWD_MS.get(world) if (n == 1024 and dtype == torch.complex64) else None
+    base_gflops = (5.0 * total * math.log2(total) / (base * 1e-3) / 1e9) if base else None
+    if rank == 0:
+        line = {
+            "metric": "pfft3d+pifft3d GFLOP/s (5*N*log2(N) per transform), 1024^3 complex64" if n == 1024 else
+                      f"pfft3d+pifft3d GFLOP/s, {n}^3",
+            "value": gflops, "unit": "GFLOP/s", "n_gpus": world, "steps": steps, "warmup": warmup,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": (gflops / base_gflops) if base_gflops else None,
+            "dtype": "complex64 (fp32)" if dtype == torch.complex64 else "complex128 (fp64)",
+            "data": "synthetic: N(0,1) real and imaginary parts, seeded per rank",
+            "impl": args.impl,
+            "config": {"model": f"pfft3d+pifft3d round trip {n}^3", "global_shape": [n, n, n], "pdims": list(pdims),
+                       "parallelism": f"{'slab' if 1 in pdims else 'pencil'} {p0}x{p1}", "backend": backend,
+                       "l2": "inputs (>= 1 GiB per GPU) are larger than the 126 MB L2; no flush needed",
+                       "baseline": "published forward-only pfft3d ms of the reference on H100 (BASELINE.md), "
+                                   "compared as GFLOP/s", "roundtrip_max_rel_err": err},
+            "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"], "reasons": clocks["reasons"]},
+            "gpu_launches": launches,
+        }
+        if e2e is not None:
+            line["e2e"] = {"value": flops / (e2e["ms_per_step"] * 1e-3) / 1e9, "unit": "GFLOP/s",
+                           "ms_per_step": e2e["ms_per_step"],
+                           "h2d_bytes_per_step": e2e["h2d_bytes_per_step"],
+                           "d2h_bytes_per_step": e2e["d2h_bytes_per_step"],
+                           "note": "input copied from pinned host memory every step (double-buffered on a copy "
+                                   "stream), one result scalar read back per step; bytes are totals over all ranks"}
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+    jd.finalize()
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -61,9 +61,10 @@ void SymmetricArena::open_peers(const std::vector<std::string>& handles) {
   }
 }
 
-void SymmetricArena::close() {
-  if (closed_) return;
-  closed_ = true;
+void SymmetricArena::close_peers() {
+  // Importers must close their mappings before the owner frees the memory, so
+  // tear-down is two-phase: every rank closes its peers' handles, the ranks
+  // synchronise on the host, and only then does each rank free its own block.
   cudaDeviceSynchronize();
   for (int p = 0; p < world_; ++p) {
     if (p == me_) continue;
@@ -71,6 +72,13 @@ void SymmetricArena::close() {
     if (flags_[p]) cudaIpcCloseMemHandle(flags_[p]);
     data_[p] = flags_[p] = nullptr;
   }
+  cudaGetLastError();
+}
+
+void SymmetricArena::close() {
+  if (closed_) return;
+  closed_ = true;
+  close_peers();
   if (data_[me_]) cudaFree(data_[me_]);
   if (flags_[me_]) cudaFree(flags_[me_]);
   data_[me_] = flags_[me_] = nullptr;

@@ -19,7 +19,8 @@ class SymmetricArena {
 
   std::string export_handles() const;                         // opaque blob to all-gather
   void open_peers(const std::vector<std::string>& handles);  // blobs of all ranks, indexed by rank
-  void close();
+  void close_peers();  // phase 1 of tear-down: unmap the other ranks' memory
+  void close();        // phase 2: free this rank's memory (also runs phase 1 if still needed)
 
   size_t bytes() const { return bytes_; }
   int world() const { return world_; }

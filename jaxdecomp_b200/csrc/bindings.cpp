@@ -11,6 +11,8 @@
 
 #include <cstring>
 #include <stdexcept>
+#include <tuple>
+#include <vector>
 
 #include "launch.h"
 #include "runtime.h"
@@ -28,6 +30,27 @@ static void raise_on(int rc, const char* what) {
   if (detail && *detail) msg += std::string(" (") + detail + ")";
   if (rc == JD_ERR_INVALID_ARG) throw py::value_error(msg);
   throw std::runtime_error(msg);
+}
+
+// regions: list of (lo0, hi0, lo1, hi1, peer, stage_off)
+static HaloDesc make_halo_desc(const std::vector<std::tuple<int, int, int, int, int, long long>>& regions, int S0, int S1,
+                               int S2, int B, int elem_bytes, int is_f64, int accumulate) {
+  HaloDesc d;
+  std::memset(&d, 0, sizeof(d));
+  if (regions.size() > 8) throw py::value_error("at most eight halo regions");
+  d.S0 = S0; d.S1 = S1; d.S2 = S2; d.B = B;
+  d.elem_bytes = elem_bytes;
+  d.is_f64 = is_f64;
+  d.accumulate = accumulate;
+  d.nregions = (int)regions.size();
+  for (size_t i = 0; i < regions.size(); ++i) {
+    HaloRegion& g = d.reg[i];
+    g.lo0 = std::get<0>(regions[i]); g.hi0 = std::get<1>(regions[i]);
+    g.lo1 = std::get<2>(regions[i]); g.hi1 = std::get<3>(regions[i]);
+    g.peer = std::get<4>(regions[i]);
+    g.stage_off = std::get<5>(regions[i]);
+  }
+  return d;
 }
 
 PYBIND11_MODULE(_jdb200, m) {
@@ -104,6 +127,7 @@ PYBIND11_MODULE(_jdb200, m) {
         for (const auto& h : hs) v.push_back((std::string)h);
         r.open_peers(v);
       })
+      .def("close_peers", &Runtime::close_peers)
       .def("destroy_arena", &Runtime::destroy_arena)
       .def("has_arena", &Runtime::has_arena)
       .def("slot_bytes", &Runtime::slot_bytes)
@@ -124,6 +148,16 @@ PYBIND11_MODULE(_jdb200, m) {
       .def("clear_plans", &Runtime::clear_plans)
       .def("execute", [](Runtime& r, int id, uintptr_t in, uintptr_t out, uintptr_t stream) {
         raise_on(r.execute(id, P(in), P(out), P(stream)), "execute");
+      })
+      .def("halo", [](Runtime& r, const std::vector<std::tuple<int, int, int, int, int, long long>>& pack,
+                      const std::vector<std::tuple<int, int, int, int, int, long long>>& unpack,
+                      const std::vector<std::tuple<int, int, int, int, int, long long>>& zero, int S0, int S1, int S2, int B,
+                      int elem_bytes, int is_f64, int accumulate, uintptr_t src, uintptr_t dst, uintptr_t stream) {
+        HaloDesc dp = make_halo_desc(pack, S0, S1, S2, B, elem_bytes, is_f64, 0);
+        HaloDesc du = make_halo_desc(unpack, S0, S1, S2, B, elem_bytes, is_f64, accumulate);
+        HaloDesc dz = make_halo_desc(zero, S0, S1, S2, B, elem_bytes, is_f64, 0);
+        const long long bytes = (long long)B * S0 * S1 * S2 * elem_bytes;
+        raise_on(r.halo(dp, du, zero.empty() ? nullptr : &dz, P(src), P(dst), bytes, P(stream)), "halo");
       })
       .def("barrier", [](Runtime& r, uintptr_t stream) { raise_on(r.barrier(P(stream)), "barrier"); })
       .def("barriers_issued", &Runtime::barriers_issued)

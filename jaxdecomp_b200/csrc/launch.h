@@ -44,15 +44,14 @@ struct HaloDesc {
   int32_t elem_bytes;      // 4, 8, 16
   int32_t nregions;
   int32_t accumulate;      // unpack: 0 overwrite, 1 add
-  int32_t pad_;
+  int32_t is_f64;          // accumulate arithmetic: 1 = float64/complex128, 0 = float32/complex64
   HaloRegion reg[8];
   void* stage[JD_MAX_PEERS];  // staging buffers (peer-visible)
   const void* src;            // local block read by pack
   void* dst;                  // local block written by unpack
 };
-// pack: for every region copy src[region] -> stage[reg.peer] + stage_off (peer stores);
-// if copy_all, also copy the whole block src -> dst in the same launch.
-int launch_halo_pack(const HaloDesc& d, int copy_all, void* stream);
+// pack: for every region copy src[region] -> stage[reg.peer] + stage_off (peer stores)
+int launch_halo_pack(const HaloDesc& d, void* stream);
 // unpack: for every region dst[region] (=|+=) stage[reg.peer] + stage_off (local loads); peer == -1 -> zero (overwrite mode)
 int launch_halo_unpack(const HaloDesc& d, void* stream);
 

@@ -42,6 +42,10 @@ void Runtime::open_peers(const std::vector<std::string>& handles) {
   arena_->open_peers(handles);
 }
 
+void Runtime::close_peers() {
+  if (arena_) arena_->close_peers();
+}
+
 void Runtime::destroy_arena() {
   if (arena_) {
     JD_TRACE_INFO("runtime", "arena destroyed");
@@ -140,6 +144,48 @@ int Runtime::execute(int plan_id, const void* in, void* out, void* stream) {
     if (is >= 0) slot_read_[is] = host_epoch_;
     if (os >= 0) slot_written_[os] = host_epoch_;
   }
+  return JD_OK;
+}
+
+int Runtime::halo(HaloDesc pack, HaloDesc unpack, const HaloDesc* zero, const void* src, void* dst, long long bytes,
+                  void* stream) {
+  const int slot = 0;
+  if (!arena_) {
+    set_last_error("runtime: halo exchange without arena");
+    return JD_ERR_INVALID_ARG;
+  }
+  int rc;
+  if (src != dst) {
+    cudaError_t e = cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyDeviceToDevice, (cudaStream_t)stream);
+    if (e != cudaSuccess) {
+      set_last_error(cudaGetErrorString(e));
+      return JD_ERR_CUDA;
+    }
+    ++launches_;
+  }
+  // nobody may still be reading the staging slot from an earlier operation
+  if (world_ > 1 && slot_read_[slot] == host_epoch_ && (rc = barrier(stream)) != JD_OK) return rc;
+  pack.src = src;
+  pack.dst = dst;
+  for (int p = 0; p < JD_MAX_PEERS; ++p) pack.stage[p] = p < world_ ? slot_ptr(slot, p) : nullptr;
+  if ((rc = launch_halo_pack(pack, stream)) != JD_OK) return rc;
+  ++launches_;
+  slot_written_[slot] = host_epoch_;
+  if (zero != nullptr) {
+    HaloDesc z = *zero;
+    z.src = src;
+    z.dst = dst;
+    for (int p = 0; p < JD_MAX_PEERS; ++p) z.stage[p] = nullptr;
+    if ((rc = launch_halo_unpack(z, stream)) != JD_OK) return rc;
+    ++launches_;
+  }
+  if (world_ > 1 && (rc = barrier(stream)) != JD_OK) return rc;
+  unpack.src = src;
+  unpack.dst = dst;
+  for (int p = 0; p < JD_MAX_PEERS; ++p) unpack.stage[p] = p < world_ ? slot_ptr(slot, p) : nullptr;
+  if ((rc = launch_halo_unpack(unpack, stream)) != JD_OK) return rc;
+  ++launches_;
+  slot_read_[slot] = host_epoch_;
   return JD_OK;
 }
 

@@ -59,6 +59,7 @@ class Runtime {
   void create_arena(size_t slot_bytes);
   std::string export_handles() const;
   void open_peers(const std::vector<std::string>& handles);
+  void close_peers();   // collective tear-down, phase 1 (host barrier needed before destroy_arena)
   void destroy_arena();
   size_t slot_bytes() const { return slot_bytes_; }
   bool has_arena() const { return (bool)arena_; }
@@ -77,6 +78,9 @@ class Runtime {
   // execution
   int execute(int plan_id, const void* in, void* out, void* stream);
   int barrier(void* stream);
+  // pack -> (zero fill) -> barrier -> unpack through arena slot 0; copies src to dst first when they differ
+  int halo(HaloDesc pack, HaloDesc unpack, const HaloDesc* zero, const void* src, void* dst, long long bytes,
+           void* stream);
   long long barriers_issued() const { return host_epoch_; }
   long long launches() const { return launches_; }
 

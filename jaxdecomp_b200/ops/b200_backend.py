@@ -1,0 +1,296 @@
+"""Native backend: executes step lists and halo exchanges with the sm_100a
+kernels of ``_jdb200``.
+
+One :class:`MeshRuntime` exists per 2-D decomposition mesh.  It owns the native
+``Runtime`` (peer-visible arena, plan cache, executor), grows the arena
+collectively when a larger problem arrives, and converts device-side status
+records into Python exceptions.  Call path of ``pfft3d`` on this backend:
+
+    ops.fft._DistFFT -> run_steps -> (cached) compile_passes/fill_desc ->
+    Runtime.execute  -> per pass: [barrier kernel] tile_pass_kernel (peer stores)
+
+The reference reaches its native executor through an XLA FFI call per op
+(``src/csrc/jaxdecomp.cc:137-179``), with plans created at lowering time; here
+plans are created on first use and looked up by a string key afterwards.
+"""
+from __future__ import annotations
+
+import atexit
+import os
+from typing import Dict, List, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+from .. import native as _native
+from ..parallel.mesh import Mesh
+from ..utils.config import config
+from ..utils.errors import KernelStatusError, PeerTimeoutError, StaleEpochError
+from . import passes as _passes
+from .plan import Step
+from .torch_backend import halo_regions
+
+_runtimes: Dict[tuple, "MeshRuntime"] = {}
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _aligned(x: torch.Tensor) -> torch.Tensor:
+    x = x.contiguous()
+    if x.data_ptr() % 16:
+        x = x.clone()
+    return x
+
+
+class MeshRuntime:
+    def __init__(self, mesh: Mesh):
+        self.nat = _native.require()
+        self.mesh = mesh
+        self.ranks = mesh.submesh_ranks()
+        self.world = len(self.ranks)
+        self.me = self.ranks.index(mesh.rank)
+        self.group = mesh.submesh_group() if self.world > 1 else None
+        self.rt = self.nat.Runtime(self.world, self.me)
+        self.rt.set_timeout_ms(int(config.wait_timeout_ms))
+        self.nat.trace_set_rank(mesh.rank)
+        self._shapes: Dict[int, tuple] = {}
+
+    # ---- arena --------------------------------------------------------------------------------
+    def ensure_arena(self, slot_bytes: int) -> None:
+        """Collective: every rank of the mesh must call this with the same size."""
+        if self.rt.has_arena() and self.rt.slot_bytes() >= slot_bytes:
+            return
+        torch.cuda.synchronize()
+        if self.world > 1:
+            if self.rt.has_arena():
+                self.rt.close_peers()
+            dist.barrier(group=self.group)
+        self.rt.create_arena(int(slot_bytes))
+        if self.world > 1:
+            blobs: List[bytes] = [b""] * self.world
+            dist.all_gather_object(blobs, self.rt.export_handles(), group=self.group)
+            self.rt.open_peers(blobs)
+            dist.barrier(group=self.group)
+
+    def release(self, collective: bool = True) -> None:
+        if not self.rt.has_arena():
+            return
+        torch.cuda.synchronize()
+        if self.world > 1 and collective and dist.is_initialized():
+            self.rt.close_peers()
+            dist.barrier(group=self.group)
+        self.rt.destroy_arena()
+
+    # ---- status ---------------------------------------------------------------------------------
+    def check_status(self, sync: bool = False) -> None:
+        if sync:
+            torch.cuda.synchronize()
+        code, peer, expected, seen, where = self.rt.read_status()
+        if code == 0:
+            return
+        self.rt.clear_status()
+        name = self.nat.status_name(code)
+        msg = (f"native kernel reported {name} (peer={peer}, expected={expected}, seen={seen}, where={where}) "
+               f"on rank {self.mesh.rank}")
+        if name == "TIMEOUT_PEER_SIGNAL":
+            raise PeerTimeoutError(msg, peer=peer, expected=expected, seen=seen)
+        if name == "STALE_EPOCH":
+            raise StaleEpochError(msg)
+        raise KernelStatusError(msg)
+
+    # ---- plans -----------------------------------------------------------------------------------
+    def _peer_arena_rank(self, mesh_axis: int, p: int) -> int:
+        coords = list(self.mesh.coords)
+        coords[self.mesh.ndim - 2 + mesh_axis] = p
+        return self.ranks.index(self.mesh.rank_of(coords))
+
+    def build_plan(self, key: str, steps: Sequence[Step], lshape, dtype, inverse: bool, scale: float, nbatch: int):
+        nat = self.nat
+        eb = torch.empty((), dtype=dtype).element_size()
+        coords = self.mesh.coords[-2:]
+        specs, final_shape = _passes.compile_passes(steps, lshape, self.mesh.pdims, coords)
+        if not specs:
+            raise ValueError("empty step list")
+        last_fft = max((i for i, s in enumerate(specs) if s.fft), default=-1)
+        n = len(specs)
+        # From which pass on can everything run in place inside the result tensor?
+        tail_plain_from = n
+        while tail_plain_from > 0 and specs[tail_plain_from - 1].plain:
+            tail_plain_from -= 1
+        bytes_per = specs[0].numel * eb * nbatch
+        plan_steps = []
+        slot_bytes = 0
+        cur_kind = nat.BUF_USER_IN
+        next_slot = nat.BUF_SLOT_A
+        for i, sp in enumerate(specs):
+            remote = sp.npeers > 1
+            d = _passes.fill_desc(nat, sp, eb, inverse, scale if i == last_fft else 1.0, nbatch, remote, True)
+            st = nat.PlanStep()
+            st.in_kind = cur_kind
+            last = i == n - 1
+            if not remote and (last or i + 1 >= tail_plain_from):
+                out_kind = nat.BUF_USER_OUT
+            else:
+                out_kind = next_slot
+                next_slot = nat.BUF_SLOT_B if next_slot == nat.BUF_SLOT_A else nat.BUF_SLOT_A
+                slot_bytes = max(slot_bytes, bytes_per)
+            st.out_kind = out_kind
+            if remote:
+                st.set_group_ranks([self._peer_arena_rank(sp.mesh_axis, p) for p in range(sp.npeers)])
+            else:
+                st.set_group_ranks([self.me])
+            st.desc = d
+            plan_steps.append(st)
+            cur_kind = out_kind
+        if cur_kind != nat.BUF_USER_OUT:
+            st = nat.PlanStep()
+            st.in_kind = cur_kind
+            st.out_kind = nat.BUF_USER_OUT
+            st.copy_only = 1
+            st.copy_bytes = bytes_per
+            plan_steps.append(st)
+        pid = self.rt.add_plan(key, plan_steps, slot_bytes)
+        return pid, final_shape
+
+    def run_steps(self, x: torch.Tensor, steps: Sequence[Step], inverse: bool, scale: float) -> torch.Tensor:
+        x = _aligned(x)
+        nb = x.dim() - 3
+        if nb not in (0, 1):
+            raise ValueError("expected a 3-D block or a 4-D block with one leading batch dimension")
+        nbatch = x.shape[0] if nb else 1
+        lshape = tuple(x.shape[nb:])
+        key = "|".join(map(str, (steps, lshape, x.dtype, bool(inverse), float(scale), nbatch, self.mesh.pdims,
+                                  self.mesh.coords[-2:], os.environ.get("JD_B200_TILE_T", ""),
+                                  os.environ.get("JD_B200_BULK", ""))))
+        pid = self.rt.find_plan(key)
+        if pid < 0:
+            pid, final_shape = self.build_plan(key, steps, lshape, x.dtype, inverse, scale, nbatch)
+            self._shapes[pid] = final_shape
+        final_shape = self._shapes[pid]
+        need = self.rt.plan_slot_bytes(pid)
+        if need > 0 or self.world > 1:
+            self.ensure_arena(max(need, 1))
+        out = torch.empty(((nbatch,) if nb else ()) + tuple(final_shape), dtype=x.dtype, device=x.device)
+        self.check_status()
+        self.rt.execute(pid, x.data_ptr(), out.data_ptr(), _stream())
+        return out
+
+    # ---- halos -------------------------------------------------------------------------------------
+    def _halo_common(self, x: torch.Tensor, extents, periods):
+        nb = x.dim() - 3
+        B = x.shape[0] if nb else 1
+        S0, S1, S2 = x.shape[nb:]
+        h0, h1 = int(extents[0]), int(extents[1])
+        p0, p1 = self.mesh.pdims
+        if p0 == 1:
+            h0 = 0
+        if p1 == 1:
+            h1 = 0
+        if (h0 and S0 < 2 * h0) or (h1 and S1 < 2 * h1):
+            raise ValueError(f"padded block {tuple(x.shape)} is smaller than twice the halo extents {(h0, h1)}")
+        regions = list(halo_regions(S0, S1, h0, h1))
+        offs, acc = [], 0
+        for (_, _, send, _recv) in regions:
+            offs.append(acc)
+            acc += B * (send[0][1] - send[0][0]) * (send[1][1] - send[1][0]) * S2
+        return nb, B, (S0, S1, S2), regions, offs, acc
+
+    def _arena_rank(self, rank):
+        return -1 if rank is None else self.ranks.index(rank)
+
+    def halo_exchange(self, x: torch.Tensor, extents, periods) -> torch.Tensor:
+        x = _aligned(x)
+        nb, B, (S0, S1, S2), regions, offs, total = self._halo_common(x, extents, periods)
+        out = torch.empty_like(x)
+        if not regions:
+            out.copy_(x)
+            return out
+        eb = x.element_size()
+        per = (bool(periods[0]), bool(periods[1]))
+        pack, unpack = [], []
+        for (d0, d1, send, recv), off in zip(regions, offs):
+            dst = self.mesh.neighbor(d0, d1, per)
+            src = self.mesh.neighbor(-d0, -d1, per)
+            pack.append((send[0][0], send[0][1], send[1][0], send[1][1], self._arena_rank(dst), off))
+            unpack.append((recv[0][0], recv[0][1], recv[1][0], recv[1][1], self.me if src is not None else -1, off))
+        self.ensure_arena(total * eb)
+        self.check_status()
+        is_f64 = int(x.dtype in (torch.float64, torch.complex128))
+        self.rt.halo(pack, unpack, [], S0, S1, S2, B, eb, is_f64, 0, x.data_ptr(), out.data_ptr(), _stream())
+        return out
+
+    def halo_accumulate(self, g: torch.Tensor, extents, periods) -> torch.Tensor:
+        g = _aligned(g)
+        nb, B, (S0, S1, S2), regions, offs, total = self._halo_common(g, extents, periods)
+        out = torch.empty_like(g)
+        if not regions:
+            out.copy_(g)
+            return out
+        eb = g.element_size()
+        per = (bool(periods[0]), bool(periods[1]))
+        pack, unpack, zero = [], [], []
+        for (d0, d1, send, recv), off in zip(regions, offs):
+            back_to = self.mesh.neighbor(-d0, -d1, per)
+            comes_from = self.mesh.neighbor(d0, d1, per)
+            pack.append((recv[0][0], recv[0][1], recv[1][0], recv[1][1], self._arena_rank(back_to), off))
+            zero.append((recv[0][0], recv[0][1], recv[1][0], recv[1][1], -1, off))
+            unpack.append((send[0][0], send[0][1], send[1][0], send[1][1],
+                           self.me if comes_from is not None else -1, off))
+        self.ensure_arena(total * eb)
+        self.check_status()
+        is_f64 = int(g.dtype in (torch.float64, torch.complex128))
+        self.rt.halo(pack, unpack, zero, S0, S1, S2, B, eb, is_f64, 1, g.data_ptr(), out.data_ptr(), _stream())
+        return out
+
+
+def get_runtime(mesh: Mesh) -> MeshRuntime:
+    key = (tuple(mesh.submesh_ranks()), mesh.pdims, torch.cuda.current_device())
+    rt = _runtimes.get(key)
+    if rt is None:
+        rt = _runtimes[key] = MeshRuntime(mesh)
+    return rt
+
+
+def run_steps(x: torch.Tensor, steps: Sequence[Step], mesh: Mesh, inverse: bool, scale: float) -> torch.Tensor:
+    return get_runtime(mesh).run_steps(x, steps, inverse, scale)
+
+
+def halo_exchange(x, extents, periods, mesh: Mesh) -> torch.Tensor:
+    return get_runtime(mesh).halo_exchange(x, extents, periods)
+
+
+def halo_accumulate(g, extents, periods, mesh: Mesh) -> torch.Tensor:
+    return get_runtime(mesh).halo_accumulate(g, extents, periods)
+
+
+def check_status(mesh: Mesh, sync: bool = True) -> None:
+    """Raise if any kernel of this mesh's runtime recorded a failure."""
+    get_runtime(mesh).check_status(sync=sync)
+
+
+def launches(mesh: Mesh) -> int:
+    """Number of kernels/copies this backend has launched on the mesh so far."""
+    return int(get_runtime(mesh).rt.launches())
+
+
+def finalize(collective: bool = True) -> None:
+    """Free every arena and forget all plans (collective when ranks > 1)."""
+    for rt in list(_runtimes.values()):
+        try:
+            rt.release(collective=collective)
+        except Exception:  # noqa: BLE001 - best effort at shutdown
+            pass
+    _runtimes.clear()
+
+
+@atexit.register
+def _at_exit():
+    # at interpreter exit the process group may be gone: free without a host barrier
+    for rt in list(_runtimes.values()):
+        try:
+            rt.release(collective=False)
+        except Exception:  # noqa: BLE001
+            pass
+    _runtimes.clear()

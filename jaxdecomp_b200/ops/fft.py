@@ -67,7 +67,7 @@ class _DistFFT(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, mesh, inverse, contiguous, scale, backend, pencil_type):
         ctx.args = (mesh, inverse, contiguous, scale, backend, pencil_type)
-        steps = _plan.fft_steps(pencil_type, inverse, contiguous)
+        steps = _plan.fft_steps(pencil_type, inverse, contiguous, native=(backend == "b200"))
         return _run(x, mesh, steps, inverse, scale, backend)
 
     @staticmethod

@@ -1,0 +1,191 @@
+"""Library life cycle, pencil geometry queries and process-grid autotuning.
+
+Parity targets in the reference's native module: ``init``/``finalize``
+(``src/csrc/jaxdecomp.cc:35-47``), ``get_pencil_info`` (``jaxdecomp.cc:53-69``),
+``get_autotuned_config`` (``jaxdecomp.cc:74-128``) and ``make_config`` =
+``GridConfig`` (``jaxdecomp.cc:617-622``).  The reference's README also shows a
+``jaxdecomp.autotune(shape=...)`` call that does not exist in its code; here
+:func:`autotune` is that convenience entry point.
+"""
+from __future__ import annotations
+
+import itertools
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..parallel.mesh import Mesh, current_mesh
+from ..parallel.sharding import PencilInfo, ShardedTensor, pencil_info
+from .config import (
+    HALO_COMM_P2P,
+    TRANSPOSE_COMM_P2P,
+    HaloCommBackend,
+    TransposeCommBackend,
+    config,
+)
+
+
+@dataclass
+class GridConfig:
+    """Global grid, process grid and transports of a decomposition."""
+
+    gdims: Tuple[int, int, int] = (0, 0, 0)
+    pdims: Tuple[int, int] = (1, 1)
+    transpose_comm_backend: TransposeCommBackend = TRANSPOSE_COMM_P2P
+    halo_comm_backend: HaloCommBackend = HALO_COMM_P2P
+
+
+def make_config(gdims=(0, 0, 0), pdims=(1, 1), transpose_comm_backend=TRANSPOSE_COMM_P2P,
+                halo_comm_backend=HALO_COMM_P2P) -> GridConfig:
+    return GridConfig(tuple(gdims), tuple(pdims), TransposeCommBackend(transpose_comm_backend),
+                      HaloCommBackend(halo_comm_backend))
+
+
+_initialised = False
+
+
+def init() -> None:
+    """Load the native core eagerly on machines with a GPU.  Optional: every op
+    initialises what it needs on first use."""
+    global _initialised
+    if torch.cuda.is_available():
+        from .. import native
+
+        native.require()
+    _initialised = True
+
+
+def finalize() -> None:
+    """Free peer-visible memory, FFT tables and cached plans.  Collective when
+    more than one rank is in use; safe to call repeatedly.  A later op simply
+    re-creates what it needs (this is also the recovery path after a reported
+    peer time-out)."""
+    global _initialised
+    try:
+        from ..ops import b200_backend
+
+        b200_backend.finalize(collective=True)
+    except Exception:  # noqa: BLE001
+        pass
+    try:
+        from .. import native
+
+        if native.is_built():
+            nat = native.load(build_if_needed=False)
+            nat.clear_fft_tables()
+            nat.trace_flush()
+    except Exception:  # noqa: BLE001
+        pass
+    _initialised = False
+
+
+def get_pencil_info(grid_config: GridConfig, axis: int, coords: Optional[Sequence[int]] = None,
+                    halo_extents: Sequence[int] = (0, 0, 0)) -> PencilInfo:
+    """Geometry (shape, lo, hi, order, halo extents, size) of this rank's pencil
+    for ``axis`` in {0: X, 1: Y, 2: Z}.  ``coords`` defaults to this rank's
+    coordinates on the active mesh."""
+    if coords is None:
+        mesh = current_mesh()
+        if mesh is not None and tuple(mesh.pdims) == tuple(grid_config.pdims):
+            coords = mesh.coords[-2:]
+        else:
+            rank = dist.get_rank() if dist.is_available() and dist.is_initialized() else 0
+            p1 = int(grid_config.pdims[1])
+            coords = ((rank // p1) % int(grid_config.pdims[0]), rank % p1)
+    return pencil_info(grid_config.gdims, grid_config.pdims, axis, coords, halo_extents)
+
+
+def _factorizations(n: int) -> List[Tuple[int, int]]:
+    return [(a, n // a) for a in range(1, n + 1) if n % a == 0]
+
+
+def _time_candidate(shape, pdims, dtype, device, iters: int, backend: str, halo=None) -> float:
+    from ..ops.fft import pfft3d, pifft3d
+    from ..ops.halo import halo_exchange
+
+    mesh = Mesh(pdims, ("z", "y"))
+    p0, p1 = pdims
+    lshape = (shape[0] // p0, shape[1] // p1, shape[2])
+    x = ShardedTensor(torch.randn(lshape, dtype=dtype, device=device), mesh)
+
+    def step():
+        if halo is None:
+            return pifft3d(pfft3d(x, backend=backend), backend=backend)
+        return halo_exchange(ShardedTensor(x.local.real.contiguous(), mesh), halo[0], halo[1], backend=backend)
+
+    step()
+    if device.type == "cuda":
+        torch.cuda.synchronize()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        for _ in range(iters):
+            step()
+        ev1.record()
+        torch.cuda.synchronize()
+        ms = ev0.elapsed_time(ev1) / iters
+    else:
+        import time
+
+        t0 = time.perf_counter()
+        for _ in range(iters):
+            step()
+        ms = (time.perf_counter() - t0) * 1e3 / iters
+    t = torch.tensor([ms], dtype=torch.float64, device=device)
+    if dist.is_available() and dist.is_initialized():
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def autotune(shape: Sequence[int], dtype: torch.dtype = torch.complex64, device=None, iters: int = 3,
+             backend: str = "auto", candidates: Optional[Sequence[Tuple[int, int]]] = None,
+             halo: Optional[Tuple[Sequence[int], Sequence[bool]]] = None, return_timings: bool = False):
+    """Time every admissible process grid ``(P0, P1)`` with ``P0*P1 == world``
+    on a round trip ``pifft3d(pfft3d(x))`` (or on a halo exchange when ``halo``
+    is given) and return the fastest, measured as the maximum over ranks.
+    Collective: all ranks must call it with the same arguments."""
+    world = dist.get_world_size() if dist.is_available() and dist.is_initialized() else 1
+    if device is None:
+        device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+    device = torch.device(device)
+    n0, n1, n2 = (int(s) for s in shape)
+    cands = list(candidates) if candidates is not None else _factorizations(world)
+    timings = {}
+    for p0, p1 in cands:
+        ok = n0 % p0 == 0 and n1 % p1 == 0 and n2 % p1 == 0 and n1 % p0 == 0 and n2 % p0 == 0
+        if not ok:
+            continue
+        timings[(p0, p1)] = _time_candidate((n0, n1, n2), (p0, p1), dtype, device, iters, backend, halo)
+    if not timings:
+        raise ValueError(f"no process grid of {world} ranks divides the global shape {tuple(shape)}")
+    best = min(timings, key=timings.get)
+    return (best, timings) if return_timings else best
+
+
+def get_autotuned_config(grid_config: GridConfig, double_precision: bool = False, disable_nccl_backends: bool = False,
+                         disable_nvshmem_backends: bool = True, tune_with_transpose: bool = True,
+                         halo_extents: Sequence[int] = (0, 0, 0),
+                         halo_periods: Sequence[bool] = (True, True, True)) -> GridConfig:
+    """Return a copy of ``grid_config`` with ``pdims`` (and both transports)
+    chosen by measurement: the transposes of an FFT round trip when
+    ``tune_with_transpose`` else a halo exchange with the given extents.  The
+    signature follows the reference's seven positional arguments; the two
+    ``disable_*`` flags select between the peer-store kernels and the NCCL
+    baseline as candidates."""
+    dtype = torch.complex128 if double_precision else torch.complex64
+    halo = None
+    if not tune_with_transpose:
+        halo = ((int(halo_extents[0]), int(halo_extents[1])), (bool(halo_periods[0]), bool(halo_periods[1])))
+    backends = ["auto"] if disable_nccl_backends else ["auto", "torch"]
+    best = None
+    for b in backends:
+        pd, timings = autotune(grid_config.gdims, dtype=dtype, backend=b, halo=halo, return_timings=True)
+        if best is None or timings[pd] < best[2]:
+            best = (pd, b, timings[pd])
+    native = best[1] == "auto" and torch.cuda.is_available()
+    from .config import HALO_COMM_NCCL, TRANSPOSE_COMM_NCCL
+
+    return GridConfig(tuple(grid_config.gdims), tuple(best[0]),
+                      TRANSPOSE_COMM_P2P if native else TRANSPOSE_COMM_NCCL,
+                      HALO_COMM_P2P if native else HALO_COMM_NCCL)

@@ -1,0 +1,108 @@
+"""Native tile passes on the CPU emulation: the planner, peer addressing and
+FFT butterflies shared with the CUDA kernels, for every decomposition, both
+layout modes, both precisions, power-of-two and arbitrary lengths."""
+import pytest
+import torch
+
+from jaxdecomp_b200 import native
+from jaxdecomp_b200.ops import emulate, plan
+from jaxdecomp_b200.parallel.mesh import pencil_type_from_pdims
+
+pytestmark = pytest.mark.skipif(not native.available(), reason="native core could not be built (no nvcc)")
+
+
+def _assemble(outs, pdims, spec, names, gshape):
+    p0, p1 = pdims
+    full = torch.zeros(gshape, dtype=outs[0].dtype)
+    for r, o in enumerate(outs):
+        c = (r // p1, r % p1)
+        idx = [slice(None)] * 3
+        for ax, s in enumerate(spec):
+            if s is not None:
+                m = names.index(s)
+                n = o.shape[ax]
+                idx[ax] = slice(c[m] * n, (c[m] + 1) * n)
+        full[tuple(idx)] = o
+    return full
+
+
+def _xspec(pdims, names):
+    return (names[0] if pdims[0] > 1 else None, names[1] if pdims[1] > 1 else None, None)
+
+
+@pytest.mark.parametrize("pdims", [(1, 1), (2, 4), (4, 2), (1, 8), (8, 1)])
+@pytest.mark.parametrize("contig", [True, False])
+@pytest.mark.parametrize("dtype,shape", [(torch.complex64, (8, 16, 32)), (torch.complex128, (24, 40, 56))])
+def test_fft_pipelines(pdims, contig, dtype, shape):
+    names = ("a0", "a1")
+    x = torch.randn(shape, dtype=dtype, generator=torch.Generator().manual_seed(0))
+    pt = pencil_type_from_pdims(pdims)
+    steps = plan.fft_steps(pt, False, contig, native=True)
+    blocks = emulate.split_blocks(x, pdims)
+    outs = emulate.emulate_steps(blocks, steps, pdims, False, 1.0)
+    _, ospec = plan.propagate(steps, blocks[0].shape, _xspec(pdims, names), pdims, names)
+    ref = torch.fft.fftn(x)
+    if contig:
+        ref = ref.permute(1, 2, 0)
+    full = _assemble(outs, pdims, ospec, names, tuple(ref.shape))
+    tol = 2e-6 if dtype == torch.complex64 else 1e-13
+    assert (full - ref).abs().max() <= tol * ref.abs().max()
+    isteps = plan.fft_steps(pt, True, contig, native=True)
+    back = emulate.emulate_steps(outs, isteps, pdims, True, 1.0 / x.numel())
+    xb = _assemble(back, pdims, _xspec(pdims, names), names, shape)
+    assert (xb - x).abs().max() <= 10 * tol * x.abs().max()
+
+
+def test_native_slab_xy_steps_equal_literal_ones():
+    # the re-ordered forward slab-XY list used by the kernels must match the literal one
+    names = ("a0", "a1")
+    x = torch.randn((8, 8, 16), dtype=torch.complex128, generator=torch.Generator().manual_seed(1))
+    ref = torch.fft.fftn(x).permute(1, 2, 0)
+    for native_list in (True, False):
+        steps = plan.fft_steps(pencil_type_from_pdims((4, 1)), False, True, native=native_list)
+        _, ospec = plan.propagate(steps, (2, 8, 16), ("a0", None, None), (4, 1), names)
+        assert ospec == (None, "a0", None)
+        if native_list:
+            outs = emulate.emulate_steps(emulate.split_blocks(x, (4, 1)), steps, (4, 1))
+            full = _assemble(outs, (4, 1), ospec, names, tuple(ref.shape))
+            assert (full - ref).abs().max() < 1e-12 * ref.abs().max()
+
+
+@pytest.mark.parametrize("contig", [True, False])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64, torch.complex64, torch.complex128])
+def test_transposes(contig, dtype):
+    names = ("a0", "a1")
+    pdims = (2, 4)
+    shape = (8, 16, 24)
+    x = torch.randn(shape, dtype=dtype, generator=torch.Generator().manual_seed(2))
+    cur = emulate.split_blocks(x, pdims)
+    spec = _xspec(pdims, names)
+    for kind, perm in (("x_y", (2, 0, 1)), ("y_z", (1, 2, 0)), ("z_y", (2, 0, 1)), ("y_x", (0, 1, 2)), ("x_z", (1, 2, 0)),
+                       ("z_x", (0, 1, 2))):
+        steps = plan.transpose_steps(kind, contig)
+        lshape = cur[0].shape
+        cur = emulate.emulate_steps(cur, steps, pdims)
+        _, spec = plan.propagate(steps, lshape, spec, pdims, names)
+        want = x.permute(perm) if contig else x
+        full = _assemble(cur, pdims, spec, names, tuple(want.shape))
+        assert torch.equal(full, want), kind
+
+
+def test_batched_blocks():
+    pdims = (2, 2)
+    names = ("a0", "a1")
+    x = torch.randn((3, 8, 8, 16), dtype=torch.complex64, generator=torch.Generator().manual_seed(3))
+    steps = plan.fft_steps(pencil_type_from_pdims(pdims), False, True, native=True)
+    outs = emulate.emulate_steps(emulate.split_blocks(x, pdims), steps, pdims)
+    ref = torch.fft.fftn(x, dim=(1, 2, 3)).permute(0, 2, 3, 1)
+    for b in range(3):
+        full = _assemble([o[b] for o in outs], pdims, ("a0", "a1", None), names, tuple(ref.shape[1:]))
+        assert (full - ref[b]).abs().max() < 1e-5 * ref.abs().max()
+
+
+def test_invalid_descriptor_is_rejected():
+    nat = native.require()
+    d = nat.PassDesc()
+    assert nat.validate_pass(d) != 0
+    with pytest.raises(ValueError):
+        nat.run_pass_host(d)

@@ -1,0 +1,110 @@
+"""Native kernels on 2+ GPUs (one process per GPU, NCCL for bootstrap):
+every op is compared elementwise with the baseline backend on the same ranks."""
+import pytest
+import torch
+
+import jaxdecomp_b200 as jd
+from jaxdecomp_b200.utils.testing import run_ranks
+
+pytestmark = pytest.mark.gpu
+
+
+def _ngpu():
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+def _pdims_list(world):
+    out = [(1, world), (world, 1)]
+    if world >= 4:
+        out += [(2, world // 2), (world // 2, 2)]
+    return out
+
+
+def _rel(a, b):
+    d = b.abs().max().clamp_min(1e-30)
+    return ((a - b).abs().max() / d).item()
+
+
+def _ops_worker(rank, world):
+    dev = torch.device("cuda", rank)
+    for pdims in _pdims_list(world):
+        mesh = jd.make_mesh(pdims, ("z", "y"))
+        p0, p1 = pdims
+        for contiguous in (True, False):
+            jd.config.update("transpose_axis_contiguous", contiguous)
+            for dtype, shape, tol in ((torch.complex64, (64, 32, 128), 3e-6), (torch.complex128, (24, 40, 56), 1e-12)):
+                g = torch.Generator(device="cpu").manual_seed(1234)
+                xg = torch.randn(shape, generator=g, dtype=torch.float64).to(dtype)
+                x = jd.shard(xg.to(dev), mesh)
+                k_ref = jd.pfft3d(x, backend="torch")
+                k = jd.pfft3d(x, backend="b200")
+                assert tuple(k.spec) == tuple(k_ref.spec) and k.local.shape == k_ref.local.shape
+                assert _rel(k.local, k_ref.local) < tol, (pdims, contiguous, dtype)
+                b = jd.pifft3d(k, backend="b200")
+                assert _rel(b.local, x.local) < 10 * tol, (pdims, contiguous, dtype)
+            # transposes, exact
+            for dtype in (torch.float32, torch.complex128):
+                xg = torch.randn((16, 32, 64), generator=torch.Generator().manual_seed(7), dtype=torch.float64).to(dtype)
+                x = jd.shard(xg.to(dev), mesh)
+                y = jd.transposeXtoY(x, backend="b200")
+                assert torch.equal(y.local, jd.transposeXtoY(x, backend="torch").local)
+                z = jd.transposeYtoZ(y, backend="b200")
+                assert torch.equal(z.local, jd.transposeYtoZ(y, backend="torch").local)
+                y2 = jd.transposeZtoY(z, backend="b200")
+                assert torch.equal(y2.local, y.local)
+                assert torch.equal(jd.transposeYtoX(y2, backend="b200").local, x.local)
+                if p0 > 1 and p1 > 1:
+                    zz = jd.transposeXtoZ(x, backend="b200")
+                    assert torch.equal(zz.local, jd.transposeXtoZ(x, backend="torch").local)
+                    assert torch.equal(jd.transposeZtoX(zz, backend="b200").local, x.local)
+        jd.config.update("transpose_axis_contiguous", True)
+        # halos: copy and accumulate, periodic and not
+        for periods in ((True, True), (False, True)):
+            for dtype in (torch.float32, torch.float64):
+                blk = torch.randn((12, 14, 10), generator=torch.Generator().manual_seed(50 + rank), dtype=dtype).to(dev)
+                st = jd.ShardedTensor(blk, mesh)
+                a = jd.halo_exchange(st, (2, 3), periods, backend="b200")
+                b = jd.halo_exchange(st, (2, 3), periods, backend="torch")
+                assert torch.equal(a.local, b.local), (pdims, periods)
+                a = jd.halo_accumulate(st, (2, 3), periods, backend="b200")
+                b = jd.halo_accumulate(st, (2, 3), periods, backend="torch")
+                torch.testing.assert_close(a.local, b.local, rtol=1e-6, atol=1e-6)
+        # gradient through the native path
+        xl = torch.randn((64 // p0, 32 // p1, 16), device=dev, requires_grad=True)
+        k = jd.pfft3d(jd.ShardedTensor(xl, mesh), backend="b200")
+        (k.local.abs() ** 2 * (rank + 1)).sum().backward()
+        xr = xl.detach().clone().requires_grad_(True)
+        kr = jd.pfft3d(jd.ShardedTensor(xr, mesh), backend="torch")
+        (kr.local.abs() ** 2 * (rank + 1)).sum().backward()
+        torch.testing.assert_close(xl.grad, xr.grad, rtol=1e-3, atol=1e-2)
+        from jaxdecomp_b200.ops import b200_backend
+
+        b200_backend.check_status(mesh, sync=True)
+        jd.finalize()
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs at least two GPUs")
+def test_native_ops_match_baseline_on_all_gpus():
+    world = 1
+    while world * 2 <= min(_ngpu(), 8):
+        world *= 2
+    run_ranks(_ops_worker, world, backend="nccl", env={"NCCL_NVLS_ENABLE": "0"}, timeout=900)
+
+
+def _barrier_worker(rank, world):
+    from jaxdecomp_b200.ops import b200_backend
+
+    mesh = jd.make_mesh((1, world), ("z", "y"))
+    rt = b200_backend.get_runtime(mesh)
+    rt.ensure_arena(1 << 20)
+    stream = torch.cuda.current_stream().cuda_stream
+    for _ in range(50):
+        rt.rt.barrier(stream)
+    torch.cuda.synchronize()
+    rt.check_status()
+    assert rt.rt.barriers_issued() == 50
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs at least two GPUs")
+def test_signal_barrier_many_rounds():
+    run_ranks(_barrier_worker, 2, backend="nccl", env={"NCCL_NVLS_ENABLE": "0"}, timeout=300)

@@ -1,0 +1,132 @@
+"""Native sm_100a kernels on one GPU against plain PyTorch references."""
+import os
+
+import pytest
+import torch
+
+import jaxdecomp_b200 as jd
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev():
+    return torch.device("cuda", 0)
+
+
+def _rel(a, b):
+    return ((a - b).abs().max() / b.abs().max()).item()
+
+
+@pytest.mark.parametrize("shape", [(64, 32, 128), (8, 16, 8), (256, 8, 1024), (16, 16, 2048), (24, 40, 58), (29, 19, 17),
+                                   (4, 2, 4096)])
+@pytest.mark.parametrize("dtype", [torch.complex64, torch.complex128])
+def test_fft_single_gpu(shape, dtype):
+    x = torch.randn(shape, device=_dev(), dtype=dtype)
+    k = jd.pfft3d(x, backend="b200")
+    ref = torch.fft.fftn(x).permute(1, 2, 0)
+    tol = 3e-6 if dtype == torch.complex64 else 1e-13
+    assert k.shape == ref.shape
+    assert _rel(k, ref) < tol
+    back = jd.pifft3d(k, backend="b200")
+    assert _rel(back, x) < 10 * tol
+    for norm in ("ortho", "forward"):
+        torch.testing.assert_close(jd.pfft3d(x, norm=norm, backend="b200"),
+                                   torch.fft.fftn(x, norm=norm).permute(1, 2, 0),
+                                   rtol=1e-4 if dtype == torch.complex64 else 1e-10,
+                                   atol=1e-4 if dtype == torch.complex64 else 1e-10)
+
+
+@pytest.mark.parametrize("bulk,tile", [("0", ""), ("1", "4"), ("1", "16"), ("0", "2")])
+def test_fft_load_paths_and_tiles(bulk, tile, monkeypatch):
+    monkeypatch.setenv("JD_B200_BULK", bulk)
+    monkeypatch.setenv("JD_B200_TILE_T", tile)
+    x = torch.randn((40, 24, 512), device=_dev(), dtype=torch.complex64)
+    k = jd.pfft3d(x, backend="b200")
+    assert _rel(k, torch.fft.fftn(x).permute(1, 2, 0)) < 3e-6
+    assert _rel(jd.pifft3d(k, backend="b200"), x) < 3e-5
+
+
+def test_fft_non_contiguous_mode_and_batch():
+    jd.config.update("transpose_axis_contiguous", False)
+    x = torch.randn((3, 16, 24, 64), device=_dev(), dtype=torch.complex64)
+    k = jd.pfft3d(x, backend="b200")
+    assert _rel(k, torch.fft.fftn(x, dim=(1, 2, 3))) < 3e-6
+    assert _rel(jd.pifft3d(k, backend="b200"), x) < 3e-5
+    jd.config.update("transpose_axis_contiguous", True)
+    k = jd.pfft3d(x, backend="b200")
+    assert _rel(k, torch.fft.fftn(x, dim=(1, 2, 3)).permute(0, 2, 3, 1)) < 3e-6
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64, torch.complex64, torch.complex128])
+def test_transposes_single_gpu(dtype):
+    x = torch.randn((12, 20, 36), device=_dev(), dtype=dtype)
+    y = jd.transposeXtoY(x, backend="b200")
+    assert torch.equal(y, x.permute(2, 0, 1))
+    z = jd.transposeYtoZ(y, backend="b200")
+    assert torch.equal(z, x.permute(1, 2, 0))
+    assert torch.equal(jd.transposeYtoX(jd.transposeZtoY(z, backend="b200"), backend="b200"), x)
+    assert torch.equal(jd.transposeZtoX(jd.transposeXtoZ(x, backend="b200"), backend="b200"), x)
+
+
+def test_fft_gradient_matches_torch():
+    x = torch.randn((16, 8, 32), device=_dev(), dtype=torch.complex128, requires_grad=True)
+    w = torch.rand((8, 32, 16), device=_dev(), dtype=torch.float64)
+    (jd.pfft3d(x, norm="ortho", backend="b200").abs().pow(2) * w).sum().backward()
+    xr = x.detach().clone().requires_grad_(True)
+    (torch.fft.fftn(xr, norm="ortho").permute(1, 2, 0).abs().pow(2) * w).sum().backward()
+    torch.testing.assert_close(x.grad, xr.grad, rtol=1e-10, atol=1e-10)
+    xf = torch.randn((16, 8, 32), device=_dev(), dtype=torch.float32, requires_grad=True)
+    jd.pifft3d(jd.pfft3d(xf, backend="b200") * 2.0, backend="b200").real.pow(2).sum().backward()
+    torch.testing.assert_close(xf.grad, 8.0 * xf.detach(), rtol=1e-4, atol=1e-4)
+
+
+def test_auto_backend_uses_native_kernels_on_cuda():
+    from jaxdecomp_b200.ops import b200_backend
+
+    mesh = jd.single_rank_mesh()
+    before = b200_backend.launches(mesh)
+    x = torch.randn((8, 8, 64), device=_dev(), dtype=torch.complex64)
+    jd.pfft3d(x)
+    assert b200_backend.launches(mesh) >= before + 3
+    b200_backend.check_status(mesh, sync=True)
+
+
+def test_bounded_wait_times_out_with_status_and_context_survives():
+    """A wait on a flag that nothing sets must end by itself with a status
+    record, leaving the CUDA context usable."""
+    from jaxdecomp_b200 import native
+    from jaxdecomp_b200.utils.errors import PeerTimeoutError
+
+    nat = native.require()
+    rt = nat.Runtime(1, 0)
+    rt.create_arena(1 << 20)
+    stream = torch.cuda.current_stream().cuda_stream
+    rt.wait_only(2, 7, 50, stream)  # two slots, epoch 7, 50 ms budget
+    torch.cuda.synchronize()
+    code, peer, expected, seen, where = rt.read_status()
+    assert nat.status_name(code) == "TIMEOUT_PEER_SIGNAL" and expected == 7 and seen == 0
+    rt.clear_status()
+    assert rt.read_status()[0] == 0
+    # the context still works
+    a = torch.ones(1024, device=_dev())
+    assert float(a.sum()) == 1024.0
+    rt.destroy_arena()
+    assert issubclass(PeerTimeoutError, RuntimeError)
+
+
+def test_large_offsets_use_64bit_indexing():
+    # 2048 x 1024 x 1024 complex64 = 16 GiB: element offsets exceed 2^31
+    free, _ = torch.cuda.mem_get_info()
+    if free < 70 * (1 << 30):
+        pytest.skip("needs ~64 GiB of free device memory")
+    n0, n1, n2 = 2048, 1024, 1024
+    x = torch.zeros((n0, n1, n2), device=_dev(), dtype=torch.complex64)
+    x[n0 - 1, n1 - 1, 5] = 1.0  # a single impulse near the end of memory
+    k = jd.pfft3d(x, backend="b200")
+    # DFT of an impulse at (a,b,c): exp(-2 pi i (a k0/n0 + b k1/n1 + c k2/n2)); output layout (k1, k2, k0)
+    k0 = torch.arange(0, n0, 397, device=_dev())
+    want = torch.exp(-2j * torch.pi * ((n1 - 1) * 3 / n1 + 5 * 7 / n2 + (n0 - 1) * k0.double() / n0)).to(torch.complex64)
+    torch.testing.assert_close(k[3, 7, k0], want, rtol=1e-4, atol=1e-4)
+    assert abs(float(k.abs().max()) - 1.0) < 1e-4
+    del k, x
+    torch.cuda.empty_cache()
