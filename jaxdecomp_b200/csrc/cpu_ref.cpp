@@ -8,7 +8,7 @@
 #include <vector>
 
 #include "launch.h"
-#include "tile_ops.h"
+#include "tile_ops.h"  // also brings fft_core.h
 
 namespace jdb {
 
@@ -21,14 +21,15 @@ static void fft_rows_host(const PassDesc& d, E* tile) {
     const int units = d.T * upr;
     std::vector<E> regs((size_t)units * 8);
     const int ns = fft_num_stages(logM);
-    int Ls = 1;
+    int logLs = 0;
     for (int s = 0; s < ns; ++s) {
       const int rl = fft_stage_radix_log(logM, s);
-      for (int u = 0; u < units; ++u) stage_read(tile + (long long)(u / upr) * d.pitch, d.M, u % upr, &regs[(size_t)u * 8]);
       for (int u = 0; u < units; ++u)
-        stage_compute_write(tile + (long long)(u / upr) * d.pitch, d.M, u % upr, Ls, rl, (const E*)d.twiddle,
-                            &regs[(size_t)u * 8]);
-      Ls <<= rl;
+        stage_read(tile + (long long)(u / upr) * d.pitch, d.M, u % upr, &regs[(size_t)u * 8], d.intra_pad);
+      for (int u = 0; u < units; ++u)
+        stage_compute_write(tile + (long long)(u / upr) * d.pitch, logM, u % upr, logLs, rl, (const E*)d.twiddle,
+                            &regs[(size_t)u * 8], d.intra_pad);
+      logLs += rl;
     }
   }
 }
@@ -44,15 +45,18 @@ static int run_pass_host_t(const PassDesc& d) {
       for (int tt = 0; tt < tiles_t; ++tt)
         for (int cc = 0; cc < tiles_c; ++cc) {
           const int t0 = tt * d.T, c0 = cc * d.Cc;
-          tile_load<E>(d, tile.data(), o, t0, c0, b, 0, 1);
+          // the data-movement phases run as an emulated block of NT threads so that
+          // the same per-thread code paths as on the GPU are exercised
+          const int NT = 64;
+          for (int tid = 0; tid < NT; ++tid) tile_load<E>(d, tile.data(), o, t0, c0, b, tid, NT);
           if (fft) {
             fft_rows_host<E>(d, tile.data());
             if (d.fft_mode == JD_FFT_BLUESTEIN) {
-              bluestein_filter<E>(d, tile.data(), 0, 1);
+              for (int tid = 0; tid < NT; ++tid) bluestein_filter<E>(d, tile.data(), tid, NT);
               fft_rows_host<E>(d, tile.data());
             }
           }
-          tile_store<E>(d, tile.data(), o, t0, c0, b, 0, 1);
+          for (int tid = 0; tid < NT; ++tid) tile_store<E>(d, tile.data(), o, t0, c0, b, tid, NT);
         }
   return JD_OK;
 }
@@ -78,7 +82,14 @@ int validate_pass(const PassDesc& d) {
   if (d.C % d.Cl || d.Tn % d.Tl || d.On % d.Ol) return JD_ERR_INVALID_ARG;
   const int np = (d.C / d.Cl) + (d.Tn / d.Tl) + (d.On / d.Ol) - 2;
   if (np != d.npeers || np < 1 || np > JD_MAX_PEERS) return JD_ERR_INVALID_ARG;
-  if (d.T < 1 || d.pitch < 1) return JD_ERR_INVALID_ARG;
+  if (d.T < 1 || d.pitch < 1 || d.logT < 0 || d.T != (1 << d.logT)) return JD_ERR_INVALID_ARG;
+  if (d.logW < 0 || (1 << d.logW) != (d.fft_mode == JD_COPY ? d.Cc : d.M)) return JD_ERR_INVALID_ARG;
+  if (d.split_axis < 0 || d.split_axis > 3) return JD_ERR_INVALID_ARG;
+  {
+    const int want = d.Cl != d.C ? 1 : (d.Tl != d.Tn ? 2 : (d.Ol != d.On ? 3 : 0));
+    if (want != d.split_axis) return JD_ERR_INVALID_ARG;
+  }
+  if (d.intra_pad && (d.fft_mode == JD_COPY || d.M < 128 || d.use_bulk)) return JD_ERR_INVALID_ARG;
   if (d.elem_bytes != 4 && d.elem_bytes != 8 && d.elem_bytes != 16) return JD_ERR_INVALID_ARG;
   if (d.load_t_contig ? d.is_t != 1 : d.is_c != 1) return JD_ERR_INVALID_ARG;
   if (d.store_t_contig ? d.os_t != 1 : d.os_c != 1) return JD_ERR_INVALID_ARG;
@@ -87,7 +98,7 @@ int validate_pass(const PassDesc& d) {
   } else {
     if (d.elem_bytes == 4) return JD_ERR_INVALID_ARG;
     if (d.M < 8 || (d.M & (d.M - 1))) return JD_ERR_INVALID_ARG;
-    if (d.pitch < d.M || !d.twiddle) return JD_ERR_INVALID_ARG;
+    if (d.pitch < padded_row_length(d.M, d.intra_pad) || !d.twiddle) return JD_ERR_INVALID_ARG;
     if (d.fft_mode == JD_FFT_POW2 && d.M != d.C) return JD_ERR_INVALID_ARG;
     if (d.fft_mode == JD_FFT_BLUESTEIN && (d.M < 2 * d.C - 1 || !d.chirp || !d.bhat)) return JD_ERR_INVALID_ARG;
   }

@@ -82,23 +82,46 @@ JD_HD int fft_stage_radix_log(int logM, int s) {
   return s < n8 ? 3 : (logM - 3 * n8);
 }
 
+// Column index -> position inside a shared-memory row.  With `pad` set, two
+// unused slots follow every 16 columns.  This makes all three exchange
+// patterns of the radix-8 stages free of bank conflicts for 8-byte elements:
+// eight consecutive outputs per thread (first stage, written as 16-byte
+// vectors), stride-8 groups (second stage) and unit stride (reads, later stages).
+JD_HD int padidx(int n, int pad) { return pad ? n + ((n >> 4) << 1) : n; }
+JD_HD int padded_row_length(int M, int pad) { return pad ? M + (M >> 3) : M; }
+
 template <typename R>
-JD_HD void stage_read(const cx<R>* row, int M, int j, cx<R> a[8]) {
+JD_HD void stage_read(const cx<R>* row, int M, int j, cx<R> a[8], int pad) {
   const int q = M >> 3;
+  if (pad) {  // q is a multiple of 16 here, so the padded offset is linear in k
+    const cx<R>* p = row + padidx(j, 1);
+    const int qp = q + (q >> 3);
 #pragma unroll
-  for (int k = 0; k < 8; ++k) a[k] = row[j + k * q];
+    for (int k = 0; k < 8; ++k) a[k] = p[k * qp];
+  } else {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) a[k] = row[j + k * q];
+  }
 }
 
-// Ls: length of the sub-transforms already done (product of earlier radices).
+template <typename R>
+struct alignas(4 * sizeof(R)) cx2 {
+  cx<R> a, b;
+};
+
+// Ls = 2^logLs: length of the sub-transforms already done (product of earlier radices).
 // tw: table of M roots exp(-2*pi*i*n/M).
 template <typename R>
-JD_HD void stage_compute_write(cx<R>* row, int M, int j, int Ls, int radix_log, const cx<R>* tw, cx<R> a[8]) {
+JD_HD void stage_compute_write(cx<R>* row, int logM, int j, int logLs, int radix_log, const cx<R>* tw, cx<R> a[8],
+                               int pad) {
+  const int M = 1 << logM;
+  const int Ls = 1 << logLs;
   const int q8 = M >> 3;
   if (radix_log == 3) {
     const int kk = j & (Ls - 1);
-    if (Ls > 1) {
-      const int ts = M / (Ls * 8);
-      const cx<R> w1 = tw[kk * ts], w2 = tw[2 * kk * ts], w4 = tw[4 * kk * ts];
+    if (logLs > 0) {
+      const int ti = kk << (logM - logLs - 3);
+      const cx<R> w1 = tw[ti], w2 = tw[2 * ti], w4 = tw[4 * ti];
       const cx<R> w3 = cmul(w1, w2), w5 = cmul(w1, w4), w6 = cmul(w2, w4);
       const cx<R> w7 = cmul(w3, w4);
       a[1] = cmul(a[1], w1); a[2] = cmul(a[2], w2); a[3] = cmul(a[3], w3); a[4] = cmul(a[4], w4);
@@ -106,35 +129,57 @@ JD_HD void stage_compute_write(cx<R>* row, int M, int j, int Ls, int radix_log, 
     }
     dft8(a);
     const int base = ((j - kk) << 3) + kk;
+    if (!pad) {
 #pragma unroll
-    for (int k = 0; k < 8; ++k) row[base + k * Ls] = a[k];
+      for (int k = 0; k < 8; ++k) row[base + (k << logLs)] = a[k];
+    } else if (logLs == 0) {
+      // eight consecutive columns inside one 16-column group: four 2-element vector stores
+      cx2<R>* p = reinterpret_cast<cx2<R>*>(row + padidx(base, 1));
+#pragma unroll
+      for (int k = 0; k < 4; ++k) p[k] = cx2<R>{a[2 * k], a[2 * k + 1]};
+    } else if (logLs == 3) {
+      cx<R>* p = row + padidx(base, 1);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) p[8 * k + 2 * (k >> 1)] = a[k];
+    } else if (logLs >= 4) {
+      cx<R>* p = row + padidx(base, 1);
+      const int lp = Ls + (Ls >> 3);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) p[k * lp] = a[k];
+    } else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) row[padidx(base + (k << logLs), 1)] = a[k];
+    }
   } else if (radix_log == 2) {
-    const int ts = M / (Ls * 4);
 #pragma unroll
     for (int m = 0; m < 2; ++m) {
       const int b = j + m * q8;
       const int kk = b & (Ls - 1);
       cx<R> x0 = a[m], x1 = a[m + 2], x2 = a[m + 4], x3 = a[m + 6];
-      if (Ls > 1) {
-        const cx<R> w1 = tw[kk * ts], w2 = tw[2 * kk * ts];
+      if (logLs > 0) {
+        const int ti = kk << (logM - logLs - 2);
+        const cx<R> w1 = tw[ti], w2 = tw[2 * ti];
         const cx<R> w3 = cmul(w1, w2);
         x1 = cmul(x1, w1); x2 = cmul(x2, w2); x3 = cmul(x3, w3);
       }
       dft4(x0, x1, x2, x3);
       const int base = ((b - kk) << 2) + kk;
-      row[base] = x0; row[base + Ls] = x1; row[base + 2 * Ls] = x2; row[base + 3 * Ls] = x3;
+      row[padidx(base, pad)] = x0;
+      row[padidx(base + Ls, pad)] = x1;
+      row[padidx(base + 2 * Ls, pad)] = x2;
+      row[padidx(base + 3 * Ls, pad)] = x3;
     }
   } else {
-    const int ts = M / (Ls * 2);
 #pragma unroll
     for (int m = 0; m < 4; ++m) {
       const int b = j + m * q8;
       const int kk = b & (Ls - 1);
       cx<R> x0 = a[m], x1 = a[m + 4];
-      if (Ls > 1) x1 = cmul(x1, tw[kk * ts]);
+      if (logLs > 0) x1 = cmul(x1, tw[kk << (logM - logLs - 1)]);
       dft2(x0, x1);
       const int base = ((b - kk) << 1) + kk;
-      row[base] = x0; row[base + Ls] = x1;
+      row[padidx(base, pad)] = x0;
+      row[padidx(base + Ls, pad)] = x1;
     }
   }
 }

@@ -20,6 +20,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdio>
+#include <cstdlib>
 #include <string>
 
 #include "launch.h"
@@ -118,34 +119,41 @@ __device__ bool tile_load_bulk(const PassDesc& d, E* tile, uint64_t* bar, int o,
 template <typename E, int ITERS>
 __device__ __forceinline__ void fft_rows(const PassDesc& d, E* tile) {
   const int M = d.M;
-  const int logM = 31 - __clz(M);
+  const int logM = d.logW;
   const int upr = M >> 3;
   const int lupr = logM - 3;
   const int units = d.T * upr;
+  const int pad = d.intra_pad;
   const E* __restrict__ tw = (const E*)d.twiddle;
   const int ns = fft_num_stages(logM);
-  int Ls = 1;
+  // the (row, butterfly) a thread owns is the same in every stage
+  E* rowp[ITERS];
+  int jj[ITERS];
+#pragma unroll
+  for (int it = 0; it < ITERS; ++it) {
+    const int u = it * blockDim.x + threadIdx.x;
+    rowp[it] = tile + (u >> lupr) * d.pitch;
+    jj[it] = u < units ? (u & (upr - 1)) : -1;
+  }
+  int logLs = 0;
   for (int s = 0; s < ns; ++s) {
     const int rl = fft_stage_radix_log(logM, s);
     E a[ITERS][8];
 #pragma unroll
-    for (int it = 0; it < ITERS; ++it) {
-      const int u = it * blockDim.x + threadIdx.x;
-      if (u < units) stage_read(tile + (long long)(u >> lupr) * d.pitch, M, u & (upr - 1), a[it]);
-    }
+    for (int it = 0; it < ITERS; ++it)
+      if (jj[it] >= 0) stage_read(rowp[it], M, jj[it], a[it], pad);
     __syncthreads();
 #pragma unroll
-    for (int it = 0; it < ITERS; ++it) {
-      const int u = it * blockDim.x + threadIdx.x;
-      if (u < units) stage_compute_write(tile + (long long)(u >> lupr) * d.pitch, M, u & (upr - 1), Ls, rl, tw, a[it]);
-    }
+    for (int it = 0; it < ITERS; ++it)
+      if (jj[it] >= 0) stage_compute_write(rowp[it], logM, jj[it], logLs, rl, tw, a[it], pad);
     __syncthreads();
-    Ls <<= rl;
+    logLs += rl;
   }
 }
 
 template <typename E, bool FFT, int ITERS>
-__global__ void tile_pass_kernel(const __grid_constant__ PassDesc d, StatusBlock* status) {
+__global__ void __launch_bounds__(FFT ? (sizeof(E) == 16 ? 256 : 512) : 256,
+                                  FFT ? (ITERS == 1 ? 3 : (ITERS == 2 ? 2 : 1)) : 4) tile_pass_kernel(const __grid_constant__ PassDesc d, StatusBlock* status) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   __shared__ uint64_t bar;
   E* tile = (E*)smem_raw;
@@ -179,23 +187,25 @@ __global__ void tile_pass_kernel(const __grid_constant__ PassDesc d, StatusBlock
 }
 
 // ---- host side ------------------------------------------------------------------------------------------------
+// Threads per block: T*M/8 butterflies spread over 1, 2 or 4 rounds per thread,
+// at most 512 threads for 8-byte elements and 256 for 16-byte ones (register budget).
 static int fft_iters(const PassDesc& d) {
-  // threads = T*M/8/iters must be a multiple of 32 in [32, 1024]
   const long long units = (long long)d.T * (d.M >> 3);
+  const long long cap = d.elem_bytes == 16 ? 256 : 512;
   for (int it : {1, 2, 4}) {
     const long long nt = (units + it - 1) / it;
-    if (nt <= 512 || it == 4) return it;
+    if (nt <= cap) return it;
   }
-  return 4;
+  return 0;
 }
 
 int pass_threads(const PassDesc& d) {
   if (d.fft_mode == JD_COPY) return 256;
   const long long units = (long long)d.T * (d.M >> 3);
   const int it = fft_iters(d);
+  if (it == 0) return 0;
   long long nt = (units + it - 1) / it;
   nt = (nt + 31) / 32 * 32;
-  if (nt > 1024) return 0;
   return (int)nt;
 }
 
@@ -209,14 +219,16 @@ static int launch_t(const PassDesc& d, cudaStream_t stream, StatusBlock* status)
     return JD_ERR_INVALID_ARG;
   }
   const size_t smem = pass_smem_bytes(d);
-  if (smem > 227 * 1024) {
-    set_last_error("tile pass: tile exceeds 227 KB of shared memory");
+  // 227 KB is the per-block limit including the kernel's small static part
+  constexpr size_t kMaxDynSmem = 226 * 1024;
+  if (smem > kMaxDynSmem) {
+    set_last_error("tile pass: tile exceeds the shared memory of one block");
     return JD_ERR_INVALID_ARG;
   }
   auto kern = tile_pass_kernel<E, FFT, ITERS>;
   static bool configured = false;  // one flag per template instantiation
   if (smem > 48 * 1024 && !configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxDynSmem);
     if (e != cudaSuccess) {
       set_last_error(cudaGetErrorString(e));
       return JD_ERR_CUDA;
@@ -247,6 +259,10 @@ int launch_pass(const PassDesc& d, void* stream_, StatusBlock* status) {
     return rc;
   }
   cudaStream_t stream = (cudaStream_t)stream_;
+  if (fast_pass_eligible(d)) {
+    const char* off = std::getenv("JD_B200_FAST");
+    if (!(off && off[0] == '0')) return launch_fast_pass(d, stream_);
+  }
   if (d.fft_mode == JD_COPY) {
     if (d.elem_bytes == 4) return launch_t<float, false, 1>(d, stream, status);
     if (d.elem_bytes == 8) return launch_t<cx<float>, false, 1>(d, stream, status);

@@ -17,6 +17,9 @@ int launch_pass(const PassDesc& d, void* stream, StatusBlock* status);
 // Threads per block the launcher will use for this descriptor (0 if invalid).
 int pass_threads(const PassDesc& d);
 size_t pass_smem_bytes(const PassDesc& d);
+// Specialised kernel for power-of-two lengths 128..4096 (fft_fast.cu)
+bool fast_pass_eligible(const PassDesc& d);
+int launch_fast_pass(const PassDesc& d, void* stream);
 
 // ---- cross-rank signalling (signal.cu) ---------------------------------------------------------------
 struct PeerFlags {

@@ -58,6 +58,10 @@ struct PassDesc {
   int32_t mul_mode;       // 0 none; 1 multiply the result by mul[] (same indexing as the output of peer 0)
   int32_t vec_in;         // 1: 8-byte elements may be loaded two at a time (16-byte accesses)
   int32_t vec_out;        // 1: 8-byte elements may be stored two at a time
+  int32_t intra_pad;      // 1: rows carry two unused slots after every 16 columns (bank-conflict-free FFT exchanges)
+  int32_t logT;           // T == 1 << logT
+  int32_t logW;           // columns held per row (M in fft modes, Cc in copy mode) == 1 << logW
+  int32_t split_axis;     // which axis selects the peer: 0 none, 1 c, 2 t, 3 o
   double scale;
   const void* in;
   void* out[JD_MAX_PEERS];

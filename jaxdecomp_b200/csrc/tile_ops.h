@@ -4,8 +4,10 @@
 // the emulation calls them with (0, 1).
 //
 // The tile is row-major [T rows][pitch], row = index along t, column = index
-// along c.  In copy mode a tile covers Cc columns starting at c0; in the FFT
-// modes it covers the whole transform axis (c0 == 0) and M >= C columns.
+// along c (through padidx() when the rows carry intra-row padding).  In copy
+// mode a tile covers Cc columns starting at c0; in the FFT modes it covers the
+// whole transform axis (c0 == 0) and M >= C columns.  T and the number of
+// columns per row are powers of two, so tile coordinates come from shifts.
 #pragma once
 #include "fft_core.h"
 
@@ -26,92 +28,85 @@ struct alignas(2 * sizeof(E)) pair_of {
   E a, b;
 };
 
+template <typename E>
+JD_HD E zero_elem() {
+  E z;
+  unsigned char* p = (unsigned char*)&z;
+  for (unsigned i = 0; i < sizeof(E); ++i) p[i] = 0;
+  return z;
+}
+
+JD_HD int tile_cols(const PassDesc& d, int c0) {
+  if (d.fft_mode != JD_COPY) return d.C;
+  return (d.C - c0) < d.Cc ? (d.C - c0) : d.Cc;
+}
+
+template <typename E>
+JD_HD E prepare_value(const PassDesc& d, E v, int c) {
+  if constexpr (elem_traits<E>::is_complex) {
+    if (d.inverse) v = cswap(v);
+    if (d.fft_mode == JD_FFT_BLUESTEIN) v = cmul(v, ((const E*)d.chirp)[c]);
+  }
+  return v;
+}
+
 // ---- load ---------------------------------------------------------------------------------
 // Rows t >= Tn (ragged last tile) and columns >= C are filled with zeros.
 template <typename E>
 JD_HD void tile_load(const PassDesc& d, E* tile, int o, int t0, int c0, int b, int tid, int nt) {
-  const E* in = (const E*)d.in;
-  const int T = d.T;
-  const int W = (d.fft_mode == JD_COPY) ? d.Cc : d.M;  // columns held per row
-  const int cols = (d.fft_mode == JD_COPY) ? ((d.C - c0) < d.Cc ? (d.C - c0) : d.Cc) : d.C;
-  const long long base = (long long)o * d.is_o + (long long)b * d.is_b;
-  E zero;
-  {
-    unsigned char* z = (unsigned char*)&zero;
-    for (unsigned i = 0; i < sizeof(E); ++i) z[i] = 0;
-  }
-  const bool blue = d.fft_mode == JD_FFT_BLUESTEIN;
-  const bool swp = d.inverse != 0;
+  const E* in = (const E*)d.in + ((long long)o * d.is_o + (long long)b * d.is_b);
+  const int T = d.T, logT = d.logT, logW = d.logW, W = 1 << logW;
+  const int cols = tile_cols(d, c0);
+  const int pad = d.intra_pad;
+  const E zero = zero_elem<E>();
   if (d.load_t_contig) {
     // lanes run along t (contiguous in memory), then along c
     if (d.vec_in && sizeof(E) == 8) {
-      const int Th = T >> 1;
-      for (int e = tid; e < Th * W; e += nt) {
-        const int c = e / Th, t = (e - c * Th) * 2;
+      const int lh = logT - 1, Th = T >> 1;
+      for (int e = tid; e < (W << lh); e += nt) {
+        const int c = e >> lh, t = (e & (Th - 1)) << 1;
         E v0 = zero, v1 = zero;
         if (c < cols && t0 + t < d.Tn) {
-          const pair_of<E> p = *(const pair_of<E>*)(in + base + (long long)(c0 + c) * d.is_c + (t0 + t));
-          v0 = p.a;
-          v1 = p.b;
-          if constexpr (elem_traits<E>::is_complex) {
-            if (swp) { v0 = cswap(v0); v1 = cswap(v1); }
-            if (blue) {
-              const E ch = ((const E*)d.chirp)[c];
-              v0 = cmul(v0, ch);
-              v1 = cmul(v1, ch);
-            }
-          }
+          const pair_of<E> p = *(const pair_of<E>*)(in + (long long)(c0 + c) * d.is_c + (t0 + t));
+          v0 = prepare_value(d, p.a, c);
+          v1 = prepare_value(d, p.b, c);
         }
-        tile[(long long)t * d.pitch + c] = v0;
-        tile[(long long)(t + 1) * d.pitch + c] = v1;
+        const int col = padidx(c, pad);
+        tile[t * d.pitch + col] = v0;
+        tile[(t + 1) * d.pitch + col] = v1;
       }
     } else {
-      for (int e = tid; e < T * W; e += nt) {
-        const int c = e / T, t = e - c * T;
+      for (int e = tid; e < (W << logT); e += nt) {
+        const int c = e >> logT, t = e & (T - 1);
         E v = zero;
-        if (c < cols && t0 + t < d.Tn) {
-          v = in[base + (long long)(c0 + c) * d.is_c + (long long)(t0 + t) * d.is_t];
-          if constexpr (elem_traits<E>::is_complex) {
-            if (swp) v = cswap(v);
-            if (blue) v = cmul(v, ((const E*)d.chirp)[c]);
-          }
-        }
-        tile[(long long)t * d.pitch + c] = v;
+        if (c < cols && t0 + t < d.Tn)
+          v = prepare_value(d, in[(long long)(c0 + c) * d.is_c + (long long)(t0 + t) * d.is_t], c);
+        tile[t * d.pitch + padidx(c, pad)] = v;
       }
     }
   } else {
     // lanes run along c (contiguous in memory)
     if (d.vec_in && sizeof(E) == 8) {
-      const int Wh = W >> 1;
-      for (int e = tid; e < T * Wh; e += nt) {
-        const int t = e / Wh, c = (e - t * Wh) * 2;
+      const int lh = logW - 1, Wh = W >> 1;
+      for (int e = tid; e < (T << lh); e += nt) {
+        const int t = e >> lh, c = (e & (Wh - 1)) << 1;
         pair_of<E> p;
         p.a = zero;
         p.b = zero;
         if (c < cols && t0 + t < d.Tn) {
-          p = *(const pair_of<E>*)(in + base + (long long)(t0 + t) * d.is_t + (c0 + c));
-          if constexpr (elem_traits<E>::is_complex) {
-            if (swp) { p.a = cswap(p.a); p.b = cswap(p.b); }
-            if (blue) {
-              p.a = cmul(p.a, ((const E*)d.chirp)[c]);
-              p.b = cmul(p.b, ((const E*)d.chirp)[c + 1]);
-            }
-          }
+          p = *(const pair_of<E>*)(in + (long long)(t0 + t) * d.is_t + (c0 + c));
+          p.a = prepare_value(d, p.a, c);
+          p.b = prepare_value(d, p.b, c + 1);
         }
-        *(pair_of<E>*)(tile + (long long)t * d.pitch + c) = p;
+        *(pair_of<E>*)(tile + t * d.pitch + padidx(c, pad)) = p;
       }
     } else {
-      for (int e = tid; e < T * W; e += nt) {
-        const int t = e / W, c = e - t * W;
+      for (int e = tid; e < (T << logW); e += nt) {
+        const int t = e >> logW, c = e & (W - 1);
         E v = zero;
-        if (c < cols && t0 + t < d.Tn) {
-          v = in[base + (long long)(t0 + t) * d.is_t + (long long)(c0 + c) * d.is_c];
-          if constexpr (elem_traits<E>::is_complex) {
-            if (swp) v = cswap(v);
-            if (blue) v = cmul(v, ((const E*)d.chirp)[c]);
-          }
-        }
-        tile[(long long)t * d.pitch + c] = v;
+        if (c < cols && t0 + t < d.Tn)
+          v = prepare_value(d, in[(long long)(t0 + t) * d.is_t + (long long)(c0 + c) * d.is_c], c);
+        tile[t * d.pitch + padidx(c, pad)] = v;
       }
     }
   }
@@ -123,9 +118,9 @@ template <typename E>
 JD_HD void tile_fixup_after_bulk(const PassDesc& d, E* tile, int tid, int nt) {
   if constexpr (elem_traits<E>::is_complex) {
     if (d.inverse) {
-      for (int e = tid; e < d.T * d.C; e += nt) {
-        const int t = e / d.C, c = e - t * d.C;
-        E* p = tile + (long long)t * d.pitch + c;
+      for (int e = tid; e < (d.T << d.logW); e += nt) {
+        const int t = e >> d.logW, c = e & ((1 << d.logW) - 1);
+        E* p = tile + t * d.pitch + c;
         *p = cswap(*p);
       }
     }
@@ -139,9 +134,9 @@ template <typename E>
 JD_HD void bluestein_filter(const PassDesc& d, E* tile, int tid, int nt) {
   if constexpr (elem_traits<E>::is_complex) {
     const E* bh = (const E*)d.bhat;
-    for (int e = tid; e < d.T * d.M; e += nt) {
-      const int t = e / d.M, m = e - t * d.M;
-      E* p = tile + (long long)t * d.pitch + m;
+    for (int e = tid; e < (d.T << d.logW); e += nt) {
+      const int t = e >> d.logW, m = e & ((1 << d.logW) - 1);
+      E* p = tile + t * d.pitch + padidx(m, d.intra_pad);
       *p = cswap(cmul(*p, bh[m]));
     }
   }
@@ -159,56 +154,92 @@ JD_HD E finish_value(const PassDesc& d, E v, int c) {
   return v;
 }
 
+// Destination of column c / row t, given the part contributed by (o, b).
+struct OutBase {
+  long long off;  // out_base + o-part + b-part
+  int peer;       // peer contribution of o
+};
+
+JD_HD OutBase out_base_for(const PassDesc& d, int o, int b) {
+  OutBase r;
+  const int po = d.split_axis == 3 ? o / d.Ol : 0;
+  r.peer = po;
+  r.off = d.out_base + (long long)(o - po * d.Ol) * d.os_o + (long long)b * d.os_b;
+  return r;
+}
+
+template <typename E>
+JD_HD E* out_ptr(const PassDesc& d, const OutBase& ob, int c, int t) {
+  const int pc = d.split_axis == 1 ? c / d.Cl : 0;
+  const int pt = d.split_axis == 2 ? t / d.Tl : 0;
+  return (E*)d.out[ob.peer + pc + pt] + (ob.off + (long long)(c - pc * d.Cl) * d.os_c + (long long)(t - pt * d.Tl) * d.os_t);
+}
+
 template <typename E>
 JD_HD void tile_store(const PassDesc& d, const E* tile, int o, int t0, int c0, int b, int tid, int nt) {
-  const int T = d.T;
-  const int cols = (d.fft_mode == JD_COPY) ? ((d.C - c0) < d.Cc ? (d.C - c0) : d.Cc) : d.C;
+  const int T = d.T, logT = d.logT, logW = d.logW, W = 1 << logW;
+  const int cols = tile_cols(d, c0);
+  const int pad = d.intra_pad;
+  const OutBase ob = out_base_for(d, o, b);
   if (d.store_t_contig) {
-    if (d.vec_out && sizeof(E) == 8) {
-      const int Th = T >> 1;
-      for (int e = tid; e < Th * cols; e += nt) {
-        const int c = e / Th, t = (e - c * Th) * 2;
-        if (t0 + t >= d.Tn) continue;
-        pair_of<E> p;
-        p.a = finish_value(d, tile[(long long)t * d.pitch + c], c0 + c);
-        p.b = finish_value(d, tile[(long long)(t + 1) * d.pitch + c], c0 + c);
-        int peer;
-        long long off;
-        out_location(d, c0 + c, t0 + t, o, b, peer, off);
-        *(pair_of<E>*)((E*)d.out[peer] + off) = p;
+    // every thread keeps its t and walks down the columns: the peer of a column
+    // is tracked incrementally instead of dividing per element
+    const bool vec = d.vec_out && sizeof(E) == 8;
+    const int lt = vec ? logT - 1 : logT;
+    const int per_col = 1 << lt;           // threads that share one column
+    if (nt % per_col == 0) {
+      const int step = nt >> lt;
+      const int tsub = tid & (per_col - 1);
+      const int t = vec ? (tsub << 1) : tsub;
+      if (t0 + t < d.Tn) {
+        const int pt = d.split_axis == 2 ? (t0 + t) / d.Tl : 0;
+        const long long toff = ob.off + (long long)(t0 + t - pt * d.Tl) * d.os_t;
+        int c = tid >> lt;
+        int pc = d.split_axis == 1 ? (c0 + c) / d.Cl : 0;
+        int cl = c0 + c - pc * d.Cl;
+        const E* src = tile + t * d.pitch;
+        for (; c < cols; c += step) {
+          E* dst = (E*)d.out[ob.peer + pc + pt] + (toff + (long long)cl * d.os_c);
+          const int col = padidx(c, pad);
+          if (vec) {
+            pair_of<E> p;
+            p.a = finish_value(d, src[col], c0 + c);
+            p.b = finish_value(d, src[d.pitch + col], c0 + c);
+            *(pair_of<E>*)dst = p;
+          } else {
+            *dst = finish_value(d, src[col], c0 + c);
+          }
+          cl += step;
+          if (d.split_axis == 1)
+            while (cl >= d.Cl) {
+              cl -= d.Cl;
+              ++pc;
+            }
+        }
       }
     } else {
-      for (int e = tid; e < T * cols; e += nt) {
-        const int c = e / T, t = e - c * T;
+      for (int e = tid; e < (cols << logT); e += nt) {
+        const int c = e >> logT, t = e & (T - 1);
         if (t0 + t >= d.Tn) continue;
-        int peer;
-        long long off;
-        out_location(d, c0 + c, t0 + t, o, b, peer, off);
-        ((E*)d.out[peer])[off] = finish_value(d, tile[(long long)t * d.pitch + c], c0 + c);
+        *out_ptr<E>(d, ob, c0 + c, t0 + t) = finish_value(d, tile[t * d.pitch + padidx(c, pad)], c0 + c);
       }
     }
   } else {
     if (d.vec_out && sizeof(E) == 8) {
-      const int Ch = cols >> 1;
-      for (int e = tid; e < T * Ch; e += nt) {
-        const int t = e / Ch, c = (e - t * Ch) * 2;
-        if (t0 + t >= d.Tn) continue;
-        pair_of<E> p = *(const pair_of<E>*)(tile + (long long)t * d.pitch + c);
+      const int lh = logW - 1, Wh = W >> 1;
+      for (int e = tid; e < (T << lh); e += nt) {
+        const int t = e >> lh, c = (e & (Wh - 1)) << 1;
+        if (c >= cols || t0 + t >= d.Tn) continue;
+        pair_of<E> p = *(const pair_of<E>*)(tile + t * d.pitch + padidx(c, pad));
         p.a = finish_value(d, p.a, c0 + c);
         p.b = finish_value(d, p.b, c0 + c + 1);
-        int peer;
-        long long off;
-        out_location(d, c0 + c, t0 + t, o, b, peer, off);
-        *(pair_of<E>*)((E*)d.out[peer] + off) = p;
+        *(pair_of<E>*)out_ptr<E>(d, ob, c0 + c, t0 + t) = p;
       }
     } else {
-      for (int e = tid; e < T * cols; e += nt) {
-        const int t = e / cols, c = e - t * cols;
-        if (t0 + t >= d.Tn) continue;
-        int peer;
-        long long off;
-        out_location(d, c0 + c, t0 + t, o, b, peer, off);
-        ((E*)d.out[peer])[off] = finish_value(d, tile[(long long)t * d.pitch + c], c0 + c);
+      for (int e = tid; e < (T << logW); e += nt) {
+        const int t = e >> logW, c = e & (W - 1);
+        if (c >= cols || t0 + t >= d.Tn) continue;
+        *out_ptr<E>(d, ob, c0 + c, t0 + t) = finish_value(d, tile[t * d.pitch + padidx(c, pad)], c0 + c);
       }
     }
   }

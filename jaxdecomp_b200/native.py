@@ -39,6 +39,7 @@ SOURCES = [
     "trace.cpp",
     "cpu_ref.cpp",
     "fft_pass.cu",
+    "fft_fast.cu",
     "signal.cu",
     "halo.cu",
     "cic.cu",

@@ -163,7 +163,8 @@ class MeshRuntime:
         lshape = tuple(x.shape[nb:])
         key = "|".join(map(str, (steps, lshape, x.dtype, bool(inverse), float(scale), nbatch, self.mesh.pdims,
                                   self.mesh.coords[-2:], os.environ.get("JD_B200_TILE_T", ""),
-                                  os.environ.get("JD_B200_BULK", ""))))
+                                  os.environ.get("JD_B200_BULK", ""), os.environ.get("JD_B200_INTRAPAD", ""),
+                                  os.environ.get("JD_B200_ROWPAD", ""), os.environ.get("JD_B200_FAST", ""))))
         pid = self.rt.find_plan(key)
         if pid < 0:
             pid, final_shape = self.build_plan(key, steps, lshape, x.dtype, inverse, scale, nbatch)

@@ -174,14 +174,21 @@ def _env_int(name: str) -> Optional[int]:
     return int(v) if v not in (None, "") else None
 
 
+def _log2(n: int) -> int:
+    return int(n).bit_length() - 1
+
+
 def choose_tiling(spec: PassSpec, elem_bytes: int, remote: bool) -> dict:
     """Pick the tile extents, shared-memory pitch and access-width flags."""
     C, Tn, On = spec.ext
     is_c, is_t, is_o = spec.in_strides
     os_c, os_t, os_o = spec.out_strides
+    Cl, Tl, Ol = spec.chunks
     load_t = is_c != 1
     store_t = os_c != 1
     out = {"load_t_contig": int(load_t), "store_t_contig": int(store_t)}
+    out["split_axis"] = 1 if Cl != C else (2 if Tl != Tn else (3 if Ol != On else 0))
+    intra_pad = 0
     if spec.fft:
         pow2 = _is_pow2(C) and C >= 8
         M = C if pow2 else max(8, _next_pow2(2 * C - 1))
@@ -189,22 +196,23 @@ def choose_tiling(spec: PassSpec, elem_bytes: int, remote: bool) -> dict:
         out["M"] = M
         if M > 16384 * 8 // elem_bytes:
             raise NotImplementedError(f"transform length {C} needs {M} points of shared memory; not supported")
-        target = 64 * 1024
+        if M >= 128 and os.environ.get("JD_B200_INTRAPAD", "1") != "0":
+            intra_pad = 1
+        rowlen = M + (M >> 3) if intra_pad else M
+        target = 80 * 1024
         T = 1
-        while T < 32 and (2 * T) * M * elem_bytes <= target and (2 * T) * M <= 32768:
+        while T < 32 and (2 * T) * rowlen * elem_bytes <= target and (2 * T) * M * elem_bytes <= 16384 * 8:
             T *= 2
-        if remote and (load_t or store_t):
-            # prefer peer stores of 128 contiguous bytes while two blocks still fit on an SM
-            want = max(1, 128 // elem_bytes)
-            while T < want and (2 * T) * (M + 4) * elem_bytes <= 96 * 1024 and (2 * T) * M <= 32768:
-                T *= 2
         T = min(T, _next_pow2(Tn))
         ov = _env_int("JD_B200_TILE_T")
         if ov:
-            T = max(1, min(ov, 32))
-            while T * M > 32768:
+            T = max(1, min(_next_pow2(ov), 32))
+            while T > 1 and (T * M * elem_bytes > 16384 * 8 or T * (rowlen + 4) * elem_bytes > 220 * 1024):
                 T //= 2
-        if not (load_t or store_t):
+        rp = _env_int("JD_B200_ROWPAD")
+        if rp is not None:
+            pad = rp
+        elif not (load_t or store_t):
             pad = 0
         elif elem_bytes == 8:
             pad = max(2, 32 // T)
@@ -213,20 +221,22 @@ def choose_tiling(spec: PassSpec, elem_bytes: int, remote: bool) -> dict:
             pad = max(1, 16 // T)
         out["T"] = T
         out["Cc"] = M
-        out["pitch"] = M + pad
+        out["pitch"] = rowlen + pad
+        out["logW"] = _log2(M)
     else:
         out["fft_mode"] = 0
         out["M"] = 0
         Cc = 64 if elem_bytes <= 8 else 32
         Cc = min(Cc, _next_pow2(C))
         T = min(32, _next_pow2(Tn))
-        if elem_bytes == 8 and (Cc & 1):
-            Cc += 1
         pad = {4: 1, 8: 2, 16: 1}[elem_bytes] if (load_t or store_t) and T > 1 else 0
         out["T"] = T
         out["Cc"] = Cc
         out["pitch"] = Cc + pad
+        out["logW"] = _log2(Cc)
     T = out["T"]
+    out["logT"] = _log2(T)
+    out["intra_pad"] = intra_pad
     vec_in = vec_out = 0
     if elem_bytes == 8 and out["pitch"] % 2 == 0:
         even = lambda *v: all(int(x) % 2 == 0 for x in v)  # noqa: E731
@@ -234,14 +244,13 @@ def choose_tiling(spec: PassSpec, elem_bytes: int, remote: bool) -> dict:
             vec_in = int(T % 2 == 0 and even(Tn, is_c, is_o))
         else:
             vec_in = int(even(C, is_t, is_o) and (spec.fft or out["Cc"] % 2 == 0))
-        Cl, Tl, Ol = spec.chunks
         if store_t:
             vec_out = int(T % 2 == 0 and even(Tn, Tl, os_c, os_o, spec.out_base))
         else:
             vec_out = int(even(C, Cl, os_t, os_o, spec.out_base) and (spec.fft or out["Cc"] % 2 == 0))
     out["vec_in"], out["vec_out"] = vec_in, vec_out
     bulk = 0
-    if spec.fft and out["fft_mode"] == 1 and not load_t and os.environ.get("JD_B200_BULK", "1") != "0":
+    if spec.fft and out["fft_mode"] == 1 and not load_t and not intra_pad and os.environ.get("JD_B200_BULK", "1") != "0":
         if (C * elem_bytes) % 16 == 0 and (is_t * elem_bytes) % 16 == 0 and (is_o * elem_bytes) % 16 == 0 \
                 and (out["pitch"] * elem_bytes) % 16 == 0:
             bulk = 1

@@ -106,3 +106,22 @@ def test_invalid_descriptor_is_rejected():
     assert nat.validate_pass(d) != 0
     with pytest.raises(ValueError):
         nat.run_pass_host(d)
+
+
+@pytest.mark.parametrize("n", [64, 128, 256, 512, 1024, 2048, 4096, 100, 384])
+@pytest.mark.parametrize("dtype", [torch.complex64, torch.complex128])
+def test_row_transforms_all_stage_structures(n, dtype):
+    """Every radix structure (8.8.2, 8.8.4, 8.8.8, ...) with intra-row padding,
+    contiguous and strided, forward and inverse."""
+    x = torch.randn((3, 4, n), dtype=dtype, generator=torch.Generator().manual_seed(n))
+    tol = 3e-6 if dtype == torch.complex64 else 1e-13
+    out = emulate.emulate_steps([x], [plan.Fft(2)], (1, 1))[0]
+    ref = torch.fft.fft(x, dim=2)
+    assert (out - ref).abs().max() <= tol * ref.abs().max()
+    out = emulate.emulate_steps([x], [plan.Fft(2), plan.Perm((2, 0, 1))], (1, 1), inverse=True)[0]
+    ref = torch.fft.ifft(x, dim=2, norm="forward").permute(2, 0, 1)
+    assert (out - ref).abs().max() <= tol * ref.abs().max()
+    y = x.permute(2, 0, 1).contiguous()  # transform along the slowest axis
+    out = emulate.emulate_steps([y], [plan.Fft(0)], (1, 1))[0]
+    ref = torch.fft.fft(y, dim=0)
+    assert (out - ref).abs().max() <= tol * ref.abs().max()

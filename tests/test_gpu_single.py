@@ -18,7 +18,7 @@ def _rel(a, b):
 
 
 @pytest.mark.parametrize("shape", [(64, 32, 128), (8, 16, 8), (256, 8, 1024), (16, 16, 2048), (24, 40, 58), (29, 19, 17),
-                                   (4, 2, 4096)])
+                                   (4, 2, 4096), (128, 128, 128), (256, 64, 512), (32, 4096, 64), (2048, 32, 256)])
 @pytest.mark.parametrize("dtype", [torch.complex64, torch.complex128])
 def test_fft_single_gpu(shape, dtype):
     x = torch.randn(shape, device=_dev(), dtype=dtype)
