@@ -161,6 +161,8 @@ class MeshRuntime:
             raise ValueError("expected a 3-D block or a 4-D block with one leading batch dimension")
         nbatch = x.shape[0] if nb else 1
         lshape = tuple(x.shape[nb:])
+        if not _passes._group_steps(steps, self.mesh.pdims):
+            return x.clone()  # every step is an exchange over a single rank: the identity
         key = "|".join(map(str, (steps, lshape, x.dtype, bool(inverse), float(scale), nbatch, self.mesh.pdims,
                                   self.mesh.coords[-2:], os.environ.get("JD_B200_TILE_T", ""),
                                   os.environ.get("JD_B200_BULK", ""), os.environ.get("JD_B200_INTRAPAD", ""),

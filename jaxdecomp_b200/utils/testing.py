@@ -35,9 +35,23 @@ def _worker(rank: int, world: int, port: int, backend: str, fn: Callable, args: 
     if backend == "nccl":
         torch.cuda.set_device(rank)
         kwargs["device_id"] = torch.device("cuda", rank)
-    dist.init_process_group(backend=backend, rank=rank, world_size=world, **kwargs)
+    import datetime
+
+    dist.init_process_group(backend=backend, rank=rank, world_size=world,
+                            timeout=datetime.timedelta(seconds=float(os.environ.get("JD_TEST_PG_TIMEOUT", "120"))), **kwargs)
     try:
-        fn(rank, world, *args)
+        try:
+            fn(rank, world, *args)
+        except BaseException:
+            # report at once and leave without collective tear-down: the other ranks may be
+            # blocked in a collective that this rank will never join
+            traceback.print_exc()
+            import sys
+
+            sys.stderr.flush()
+            if backend == "nccl":
+                os._exit(1)
+            raise
         if backend == "nccl":
             torch.cuda.synchronize()
             try:
