@@ -44,6 +44,7 @@ SOURCES = [
     "halo.cu",
     "cic.cu",
     "kspace.cu",
+    "no_alloc.cu",
 ]
 
 NVCC_FLAGS = [
