@@ -176,6 +176,40 @@ PYBIND11_MODULE(_jdb200, m) {
       .def_property_readonly("world", &Runtime::world)
       .def_property_readonly("me", &Runtime::me);
 
+
+  // ---- particle-mesh and k-space kernels -------------------------------------------------------------------
+  m.def("cic", [](int op, long long n, std::vector<int> S, std::vector<int> wrap, std::vector<int> grid,
+                  std::vector<float> origin, float wscalar, uintptr_t pos, uintptr_t weight, uintptr_t mesh, uintptr_t out,
+                  uintptr_t stream) {
+    if (S.size() != 3 || wrap.size() != 3 || grid.size() != 3 || origin.size() != 3) throw py::value_error("cic: 3-vectors expected");
+    CicArgs a;
+    a.n = n;
+    a.S0 = S[0]; a.S1 = S[1]; a.S2 = S[2];
+    a.wrap0 = wrap[0]; a.wrap1 = wrap[1]; a.wrap2 = wrap[2];
+    a.g0 = grid[0]; a.g1 = grid[1]; a.g2 = grid[2];
+    a.o0 = origin[0]; a.o1 = origin[1]; a.o2 = origin[2];
+    a.wscalar = wscalar;
+    int rc;
+    if (op == 0) rc = launch_cic_paint(a, (const float*)P(pos), (const float*)P(weight), (float*)P(mesh), P(stream));
+    else if (op == 1) rc = launch_cic_readout(a, (const float*)P(pos), (const float*)P(mesh), (float*)P(out), P(stream));
+    else rc = launch_cic_paint_grad_pos(a, (const float*)P(pos), (const float*)P(weight), (const float*)P(mesh), (float*)P(out), P(stream));
+    raise_on(rc, "cic");
+  });
+  m.def("kspace", [](int mode, std::vector<int> L, std::vector<int> off, std::vector<int> N, std::vector<float> box,
+                     std::vector<float> prm, int ntable, uintptr_t table, uintptr_t in, uintptr_t out0, uintptr_t out1,
+                     uintptr_t out2, uintptr_t stream) {
+    if (L.size() != 3 || off.size() != 3 || N.size() != 3 || box.size() != 3 || prm.size() != 4) throw py::value_error("kspace: bad argument sizes");
+    KSpaceDesc d;
+    d.L0 = L[0]; d.L1 = L[1]; d.L2 = L[2];
+    d.off0 = off[0]; d.off1 = off[1]; d.off2 = off[2];
+    d.N0 = N[0]; d.N1 = N[1]; d.N2 = N[2];
+    d.mode = mode;
+    d.ntable = ntable;
+    d.box0 = box[0]; d.box1 = box[1]; d.box2 = box[2];
+    d.p0 = prm[0]; d.p1 = prm[1]; d.p2 = prm[2]; d.p3 = prm[3];
+    raise_on(launch_kspace(d, P(in), P(out0), P(out1), P(out2), (const float*)P(table), P(stream)), "kspace");
+  });
+
   // ---- trace log / profiler ------------------------------------------------------------------------------
   m.def("trace_enabled", [](const std::string& logger, int level) { return trace_enabled(logger.c_str(), (TraceLevel)level); });
   m.def("trace_write", [](const std::string& logger, int level, const std::string& msg) {

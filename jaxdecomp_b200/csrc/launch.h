@@ -59,14 +59,19 @@ int launch_halo_pack(const HaloDesc& d, void* stream);
 int launch_halo_unpack(const HaloDesc& d, void* stream);
 
 // ---- particle-mesh kernels (cic.cu) ---------------------------------------------------------------------
-// pos: [n,3] positions in units of cells relative to the origin of the local (padded) mesh
-int launch_cic_paint(const float* pos, const float* weight, long long n, float* mesh, int S0, int S1, int S2,
-                     int wrap0, int wrap1, int wrap2, void* stream);
-int launch_cic_readout(const float* pos, long long n, const float* mesh, float* out, int S0, int S1, int S2, int wrap0,
-                       int wrap1, int wrap2, void* stream);
-// gradient of paint w.r.t. positions: gpos[n,3] = sum over 8 cells of gmesh * d(weight)/d(pos) * w
-int launch_cic_paint_grad_pos(const float* pos, const float* weight, long long n, const float* gmesh, float* gpos,
-                              int S0, int S1, int S2, int wrap0, int wrap1, int wrap2, void* stream);
+struct CicArgs {
+  long long n;               // number of particles
+  int32_t S0, S1, S2;        // local (padded) mesh block
+  int32_t wrap0, wrap1, wrap2;
+  int32_t g0, g1, g2;        // lattice of initial positions (grid mode: pos holds displacements), or 0
+  float o0, o1, o2;          // offset of the lattice inside the block
+  float wscalar;             // weight of every particle when no per-particle weights are given
+};
+// pos: [n,3] float32 positions (or displacements in grid mode) in cell units
+int launch_cic_paint(const CicArgs& a, const float* pos, const float* weight, float* mesh, void* stream);
+int launch_cic_readout(const CicArgs& a, const float* pos, const float* mesh, float* out, void* stream);
+int launch_cic_paint_grad_pos(const CicArgs& a, const float* pos, const float* weight, const float* gmesh, float* gpos,
+                              void* stream);
 
 // ---- k-space elementwise kernels (kspace.cu) --------------------------------------------------------------
 struct KSpaceDesc {
@@ -75,10 +80,12 @@ struct KSpaceDesc {
   int32_t off0, off1, off2;  // global index of the first local element on each dim
   int32_t N0, N1, N2;        // global extents of the *original* axes 0, 1, 2
   int32_t mode;              // see kspace.cu
+  int32_t ntable;            // mode 1: number of samples of the power-spectrum table
   float box0, box1, box2;    // physical box lengths along original axes
-  float p0, p1, p2, p3;      // mode-specific parameters
+  float p0, p1, p2, p3;      // mode 0: amplitude, index, cut-off, normalisation; mode 1: log k0, d log k, -, normalisation
 };
-int launch_kspace(const KSpaceDesc& d, const void* in, void* out0, void* out1, void* out2, void* stream);
+int launch_kspace(const KSpaceDesc& d, const void* in, void* out0, void* out1, void* out2, const float* table,
+                  void* stream);
 
 // ---- misc --------------------------------------------------------------------------------------------
 const char* last_error_message();

@@ -91,6 +91,36 @@ def test_native_ops_match_baseline_on_all_gpus():
     run_ranks(_ops_worker, world, backend="nccl", env={"NCCL_NVLS_ENABLE": "0"}, timeout=900)
 
 
+def _lpt_worker(rank, world):
+    from jaxdecomp_b200.models.lpt import LPTConfig, LPTModel, lpt_loss
+
+    dev = torch.device("cuda", rank)
+    for pdims in _pdims_list(world)[:2] + _pdims_list(world)[2:3]:
+        mesh = jd.make_mesh(pdims, ("z", "y"))
+        noise_g = torch.randn((32, 32, 32), generator=torch.Generator().manual_seed(0))
+        res = {}
+        for backend in ("b200", "torch"):
+            cfg = LPTConfig(nc=32, box_size=32.0, halo=4, amplitude=0.05, backend=backend)
+            noise = jd.shard(noise_g.to(dev), mesh)
+            noise.local.requires_grad_(True)
+            model = LPTModel(mesh, cfg)
+            loss = lpt_loss(model, noise)
+            loss.backward()
+            res[backend] = (float(loss), noise.local.grad.clone(), model(noise).local.detach())
+        assert abs(res["b200"][0] - res["torch"][0]) < 1e-4 * abs(res["torch"][0])
+        assert _rel(res["b200"][2], res["torch"][2]) < 1e-3
+        assert _rel(res["b200"][1], res["torch"][1]) < 5e-3
+        jd.finalize()
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs at least two GPUs")
+def test_lpt_step_native_vs_baseline_multi_gpu():
+    world = 1
+    while world * 2 <= min(_ngpu(), 8):
+        world *= 2
+    run_ranks(_lpt_worker, world, backend="nccl", env={"NCCL_NVLS_ENABLE": "0"}, timeout=600)
+
+
 def _barrier_worker(rank, world):
     from jaxdecomp_b200.ops import b200_backend
 
