@@ -3,6 +3,7 @@
 
 #include <cuda_runtime.h>
 
+#include <cstdio>
 #include <stdexcept>
 
 #include "trace.h"
@@ -92,6 +93,16 @@ void Runtime::clear_plans() {
 int Runtime::barrier(void* stream) {
   if (world_ == 1) return JD_OK;
   if (!arena_) throw std::runtime_error("runtime: barrier without arena");
+  StepProfiler& prof = StepProfiler::instance();
+  struct Scope {
+    StepProfiler& p;
+    void* s;
+    bool on;
+    ~Scope() {
+      if (on) p.stop(s);
+    }
+  } scope{prof, stream, prof.mode() != StepProfiler::OFF};
+  if (scope.on) prof.start("barrier", stream);
   PeerFlags pf;
   for (int p = 0; p < JD_MAX_PEERS; ++p) pf.flags[p] = p < world_ ? flag_ptr(p) : nullptr;
   ++host_epoch_;
@@ -121,6 +132,17 @@ int Runtime::execute(int plan_id, const void* in, void* out, void* stream) {
       if (rc != JD_OK) return rc;
     }
     const void* src = st.in_kind == BUF_USER_IN ? in : (st.in_kind == BUF_USER_OUT ? out : slot_ptr(is, me_));
+    StepProfiler& prof = StepProfiler::instance();
+    const bool profiling = prof.mode() != StepProfiler::OFF;
+    if (profiling) {
+      char name[96];
+      if (st.copy_only)
+        std::snprintf(name, sizeof(name), "plan%d.step%d copy", plan_id, (int)(&st - &pl.steps[0]));
+      else
+        std::snprintf(name, sizeof(name), "plan%d.step%d %s C=%d peers=%d", plan_id, (int)(&st - &pl.steps[0]),
+                      st.desc.fft_mode == JD_COPY ? "copy-pass" : "fft-pass", st.desc.C, st.desc.npeers);
+      prof.start(name, stream);
+    }
     if (st.copy_only) {
       void* dst = st.out_kind == BUF_USER_OUT ? out : slot_ptr(os, me_);
       cudaError_t e = cudaMemcpyAsync(dst, src, (size_t)st.copy_bytes, cudaMemcpyDeviceToDevice, (cudaStream_t)stream);
@@ -140,6 +162,7 @@ int Runtime::execute(int plan_id, const void* in, void* out, void* stream) {
       int rc = launch_pass(d, stream, status_device());
       if (rc != JD_OK) return rc;
     }
+    if (profiling) prof.stop(stream);
     ++launches_;
     if (is >= 0) slot_read_[is] = host_epoch_;
     if (os >= 0) slot_written_[os] = host_epoch_;
