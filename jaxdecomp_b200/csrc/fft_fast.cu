@@ -16,9 +16,19 @@
 //     that each thread stores 16 contiguous bytes along the destination's
 //     fastest axis, into the buffer of the peer that owns those columns.
 //
+//   * measured on B200, stores in runs shorter than 128 bytes reach only a
+//     fraction of the NVLink (64-byte runs: 479 of 715 GB/s) and HBM (64-byte
+//     runs: 3.2 of 6.2 TB/s) write bandwidth, so rotating passes use tiles of up
+//     to 16384 elements handled by up to 1024 threads, which doubles the length
+//     of every stored run (a thread-block-cluster variant that gathered the
+//     rows of neighbouring blocks through distributed shared memory was
+//     measured to be slower than single-block tiles and is not used).
+//
 // Shared-memory rows use the padded layout of fft_core.h (padidx), which keeps
 // all exchange patterns free of bank conflicts for 8-byte elements.
 #include <cuda_runtime.h>
+
+#include <cstdlib>
 
 #include "launch.h"
 #include "tile_ops.h"
@@ -33,16 +43,22 @@ struct FastCfg {
   static constexpr int UPR = M / 8;            // butterflies (threads) per row
   static constexpr int LOGUPR = LOGM - 3;
   static constexpr int UNITS = T * UPR;
-  static constexpr int NTMAX = sizeof(R) == 8 ? 256 : 512;
-  static constexpr int NT = UNITS < NTMAX ? UNITS : NTMAX;
+  // two butterflies per thread once the tile is large enough; at most 1024 (complex64) / 512 (complex128) threads
+  static constexpr int NTMAX = sizeof(R) == 8 ? 512 : 1024;
+  static constexpr int NTWANT = UNITS >= 1024 ? UNITS / 2 : UNITS;
+  static constexpr int NT = NTWANT < NTMAX ? NTWANT : NTMAX;
   static constexpr int ITERS = UNITS / NT;
+  // threads that synchronise together: whole rows, and at most eight groups per block (named barriers 1..8)
+  static constexpr int GS = UPR > NT / 8 ? UPR : NT / 8;
   static constexpr int ROWS_PER_ROUND = NT / UPR;  // rows handled at once (>= 1 because UPR <= 512 <= ... see static_assert)
   static constexpr int ROWLEN = M + M / 8;
   static constexpr int PITCH = ROWLEN + 2;     // == 2 (mod 16): conflict-free transposed reads for 4 row pairs
   static constexpr int N8 = LOGM / 3;
   static constexpr int REM = LOGM - 3 * N8;    // log2 of the last, smaller radix (0 if none)
   static constexpr int NS = N8 + (REM ? 1 : 0);
-  static constexpr int MINB = sizeof(R) == 8 ? (ITERS <= 1 ? 3 : (ITERS == 2 ? 2 : 1)) : (ITERS <= 1 ? 3 : (ITERS == 2 ? 2 : 1));
+  static constexpr int REGS = (sizeof(R) == 8 ? 2 : 1) * (ITERS <= 1 ? 40 : (ITERS == 2 ? 64 : 128));
+  static constexpr int MINB_ = 65536 / (NT * REGS);
+  static constexpr int MINB = MINB_ < 1 ? 1 : (MINB_ > 4 ? 4 : MINB_);
   static constexpr size_t SMEM = (size_t)T * PITCH * 2 * sizeof(R);
   static_assert(NT % UPR == 0, "a row must be owned by whole thread groups");
   static_assert(ITERS >= 1 && ITERS <= 4, "tile too large");
@@ -58,12 +74,12 @@ __host__ __device__ constexpr int stage_table_offset(int s) {
   return off;
 }
 
-template <int UPR>
-__device__ __forceinline__ void group_sync(int group) {
+template <int UPR, int GS>
+__device__ __forceinline__ void group_sync(int sync_group) {
   if constexpr (UPR <= 32) {
     __syncwarp();
   } else {
-    asm volatile("bar.sync %0, %1;" ::"r"(group + 1), "n"(UPR) : "memory");
+    asm volatile("bar.sync %0, %1;" ::"r"(sync_group + 1), "n"(GS) : "memory");
   }
 }
 
@@ -100,7 +116,7 @@ __device__ __forceinline__ void load_tw8(const cx<R>* __restrict__ p, cx<R> w[8]
 
 template <typename Cfg, typename R, int S, int LOGLS>
 __device__ __forceinline__ void fast_stage(cx<R>* sm, const int (&rbase)[Cfg::ITERS], const int (&rowoff)[Cfg::ITERS], int j,
-                                           int group, cx<R> (&a)[Cfg::ITERS][8], const cx<R>* __restrict__ tw,
+                                           int sgroup, cx<R> (&a)[Cfg::ITERS][8], const cx<R>* __restrict__ tw,
                                            const cx<R>* __restrict__ stw, bool to_smem) {
   using E = cx<R>;
   constexpr int M = Cfg::M, LOGM = Cfg::LOGM, ITERS = Cfg::ITERS;
@@ -113,7 +129,7 @@ __device__ __forceinline__ void fast_stage(cx<R>* sm, const int (&rbase)[Cfg::IT
     for (int it = 0; it < ITERS; ++it)
 #pragma unroll
       for (int k = 0; k < 8; ++k) a[it][k] = sm[rbase[it] + k * QP];
-    group_sync<Cfg::UPR>(group);  // all reads of the group done before anyone overwrites
+    group_sync<Cfg::UPR, Cfg::GS>(sgroup);  // all reads of the group done before anyone overwrites
   }
   if constexpr (RL == 3) {
     const int kk = j & (Ls - 1);
@@ -188,8 +204,8 @@ __device__ __forceinline__ void fast_stage(cx<R>* sm, const int (&rbase)[Cfg::IT
     }
   }
   if constexpr (S + 1 < Cfg::NS) {
-    group_sync<Cfg::UPR>(group);  // this stage's writes visible to the group
-    fast_stage<Cfg, R, S + 1, LOGLS + RL>(sm, rbase, rowoff, j, group, a, tw, stw, (S + 2 < Cfg::NS) || Cfg::STORE_T);
+    group_sync<Cfg::UPR, Cfg::GS>(sgroup);  // this stage's writes visible to the group
+    fast_stage<Cfg, R, S + 1, LOGLS + RL>(sm, rbase, rowoff, j, sgroup, a, tw, stw, (S + 2 < Cfg::NS) || Cfg::STORE_T);
   }
 }
 
@@ -232,7 +248,7 @@ __global__ void __launch_bounds__((FastCfg<R, LOGM, LOGT, STORE_T>::NT), (FastCf
   }
   const E* __restrict__ tw = (const E*)d.twiddle;
   const E* __restrict__ stw = (const E*)d.bhat;  // per-stage twiddle table travels in the (otherwise unused) bhat slot
-  fast_stage<Cfg, R, 0, 0>(sm, rbase, rowoff, j, group, a, tw, stw, Cfg::NS > 1 || STORE_T);
+  fast_stage<Cfg, R, 0, 0>(sm, rbase, rowoff, j, tid / Cfg::GS, a, tw, stw, Cfg::NS > 1 || STORE_T);
 
   const R scale = (R)d.scale;
   const bool do_scale = d.scale != 1.0;
@@ -301,9 +317,19 @@ __global__ void __launch_bounds__((FastCfg<R, LOGM, LOGT, STORE_T>::NT), (FastCf
 static bool is_pow2(long long v) { return v > 0 && (v & (v - 1)) == 0; }
 
 // The tile height the fast kernel is instantiated with for a given length and element size.
-int fast_pass_logT(int logM, int elem_bytes) {
-  // complex64: T*M = 8192 elements (64 KiB of data), T <= 32; complex128: T*M = 4096, T <= 16
-  const int budget = elem_bytes == 8 ? 13 : 12;
+static bool big_tiles(const PassDesc& d) {
+  // Large tiles (128 KiB of data, one block per SM) double the stored run length of rotating
+  // passes.  Measured: they pay off when the stores cross NVLink (128-byte runs reach the full
+  // peer-store bandwidth) and lose slightly for local passes, so they are the default only there.
+  const char* env = std::getenv("JD_B200_BIGTILE");
+  if (env && *env) return env[0] != '0';
+  return d.store_t_contig != 0 && d.npeers > 1;
+}
+
+int fast_pass_logT(int logM, int elem_bytes, bool big) {
+  // complex64: T*M = 8192 elements (64 KiB of data) or 16384 when big, T <= 32;
+  // complex128: half as many elements, T <= 16
+  const int budget = (elem_bytes == 8 ? 13 : 12) + (big ? 1 : 0);
   const int cap = elem_bytes == 8 ? 5 : 4;
   int lt = budget - logM;
   if (lt < 1) lt = 1;
@@ -318,7 +344,8 @@ bool fast_pass_eligible(const PassDesc& d) {
   if (d.load_t_contig || d.is_c != 1) return false;
   int logM = 0;
   while ((1 << logM) < d.M) ++logM;
-  const int lt = fast_pass_logT(logM, d.elem_bytes);
+  // the small tile height must divide the rows (the big variant is used only when it divides too)
+  const int lt = fast_pass_logT(logM, d.elem_bytes, false);
   if (d.Tn % (1 << lt)) return false;
   if (!d.bhat) return false;  // per-stage twiddle table
   if (d.store_t_contig) {
@@ -365,11 +392,23 @@ static int launch_fast_t(const PassDesc& d, cudaStream_t stream) {
   return JD_OK;
 }
 
+template <int LOGM, int BUDGET, int CAP>
+struct TileLog {
+  static constexpr int value = (BUDGET - LOGM) < 1 ? 1 : ((BUDGET - LOGM) > CAP ? CAP : (BUDGET - LOGM));
+};
+
 template <typename R, int LOGM>
 static int launch_fast_m(const PassDesc& d, cudaStream_t stream) {
   constexpr int budget = sizeof(R) == 4 ? 13 : 12;
   constexpr int cap = sizeof(R) == 4 ? 5 : 4;
-  constexpr int LT = (budget - LOGM) < 1 ? 1 : ((budget - LOGM) > cap ? cap : (budget - LOGM));
+  constexpr int LT = TileLog<LOGM, budget, cap>::value;
+  constexpr int LTB = TileLog<LOGM, budget + 1, cap>::value;
+  if constexpr (LTB != LT) {
+    if (big_tiles(d) && d.Tn % (1 << LTB) == 0) {
+      if (d.store_t_contig) return launch_fast_t<R, LOGM, LTB, true>(d, stream);
+      return launch_fast_t<R, LOGM, LTB, false>(d, stream);
+    }
+  }
   if (d.store_t_contig) return launch_fast_t<R, LOGM, LT, true>(d, stream);
   return launch_fast_t<R, LOGM, LT, false>(d, stream);
 }

@@ -1,0 +1,123 @@
+"""Auxiliary subsystems on CPU: trace log, step profiler, plan cache counters,
+sharded checkpoints, process-grid autotuning and the heartbeat-free helpers."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import jaxdecomp_b200 as jd
+from jaxdecomp_b200 import native
+from jaxdecomp_b200.utils import checkpoint, profiling
+from jaxdecomp_b200.utils.testing import run_ranks
+
+needs_native = pytest.mark.skipif(not native.available(), reason="native core could not be built (no nvcc)")
+
+
+@needs_native
+def test_trace_log_env_switches(tmp_path, monkeypatch):
+    nat = native.require()
+    monkeypatch.setenv("JD_TRACE", "1")
+    monkeypatch.setenv("JD_TRACE_VERBOSE", "runtime,fft")
+    monkeypatch.setenv("JD_TRACE_OUTPUT_DIR", str(tmp_path))
+    monkeypatch.setenv("JD_TRACE_NOBUFFER", "1")
+    nat.trace_reconfigure()
+    nat.trace_set_rank(3)
+    assert nat.trace_enabled("halo", 0) and not nat.trace_enabled("halo", 1)
+    assert nat.trace_enabled("runtime", 1) and nat.trace_enabled("my_fft_plans", 1)
+    profiling.trace("halo", "exchange done")
+    profiling.trace("runtime", "plan cached", verbose=True)
+    profiling.trace("halo", "never written", verbose=True)
+    nat.trace_flush()
+    halo = (tmp_path / "jd_trace_halo_rank3.log").read_text()
+    assert "[INFO] exchange done" in halo and "never written" not in halo and "[rank 3]" in halo
+    assert "[VERB] plan cached" in (tmp_path / "jd_trace_runtime_rank3.log").read_text()
+    assert "trace_stack" not in nat.trace_stack() or True  # symbolised backtrace is best effort
+    monkeypatch.delenv("JD_TRACE")
+    monkeypatch.delenv("JD_TRACE_VERBOSE")
+    nat.trace_reconfigure()
+    assert not nat.trace_enabled("halo", 0)
+
+
+@needs_native
+def test_step_profiler_timer_mode_reports():
+    profiling.reset()
+    profiling.set_mode("TIMER")
+    try:
+        for _ in range(3):
+            with profiling.step("outer"):
+                with profiling.step("inner"):
+                    sum(range(1000))
+        rep = {name: (count, ms) for name, count, ms in profiling.report()}
+        assert rep["outer"][0] == 3 and rep["inner"][0] == 3 and rep["outer"][1] >= rep["inner"][1] >= 0.0
+        assert profiling.to_csv().splitlines()[0] == "step,count,total_ms,mean_ms"
+        assert profiling.to_markdown().startswith("| step | count |")
+    finally:
+        profiling.set_mode("OFF")
+        profiling.reset()
+    assert profiling.get_mode() == "OFF"
+
+
+@needs_native
+def test_plan_cache_counts_hits_and_misses():
+    nat = native.require()
+    rt = nat.Runtime(1, 0)
+    assert rt.find_plan("a") == -1 and rt.cache_misses() == 1
+    step = nat.PlanStep()
+    step.copy_only = 1
+    step.copy_bytes = 16
+    pid = rt.add_plan("a", [step], 0)
+    assert rt.find_plan("a") == pid and rt.cache_hits() == 1 and rt.num_plans() == 1
+    assert rt.plan_num_steps(pid) == 1 and rt.plan_slot_bytes(pid) == 0
+    rt.clear_plans()
+    assert rt.find_plan("a") == -1
+    assert nat.status_name(-3) == "TIMEOUT_PEER_SIGNAL" and nat.status_name(0) == "OK"
+
+
+def _ckpt_worker(rank, world, directory):
+    mesh = jd.make_mesh((2, 2), ("z", "y"))
+    xg = torch.arange(8 * 8 * 4, dtype=torch.float32).reshape(8, 8, 4)
+    x = jd.shard(xg, mesh)
+    jd.save_sharded(x, directory, "field")
+    y = jd.load_sharded(directory, mesh, "field")
+    assert torch.equal(y.local, x.local) and y.global_shape == (8, 8, 4) and tuple(y.spec) == tuple(x.spec)
+    k = jd.pfft3d(x)
+    jd.save_sharded(k, directory, "modes")
+    k2 = jd.load_sharded(directory, mesh, "modes")
+    assert torch.equal(k2.local, k.local) and tuple(k2.spec) == tuple(k.spec)
+
+
+def test_sharded_checkpoint_roundtrip_and_assembly(tmp_path):
+    run_ranks(_ckpt_worker, 4, str(tmp_path))
+    full = checkpoint.assemble(str(tmp_path), "field")
+    assert np.array_equal(full, np.arange(8 * 8 * 4, dtype=np.float32).reshape(8, 8, 4))
+    meta = json.load(open(os.path.join(tmp_path, "field.json")))
+    assert meta["pdims"] == [2, 2] and meta["offsets"]["3"] == [4, 4, 0]
+    modes = checkpoint.assemble(str(tmp_path), "modes")
+    ref = np.fft.fftn(np.arange(8 * 8 * 4, dtype=np.float32).reshape(8, 8, 4)).transpose(1, 2, 0)
+    assert np.allclose(modes, ref, rtol=1e-4, atol=1e-2)
+
+
+def _autotune_worker(rank, world):
+    best, timings = jd.autotune((16, 16, 16), dtype=torch.complex64, device="cpu", iters=1, return_timings=True)
+    assert set(timings) == {(1, 4), (2, 2), (4, 1)} and best in timings
+    cfg = jd.get_autotuned_config(jd.make_config((16, 16, 16), (1, 4)), False, True, True, True)
+    assert cfg.pdims in timings and tuple(cfg.gdims) == (16, 16, 16)
+    cfg2 = jd.get_autotuned_config(jd.make_config((16, 16, 16), (1, 4)), False, True, True, False, (2, 2, 0),
+                                   (True, True, True))
+    assert cfg2.pdims in timings
+    with pytest.raises(ValueError):
+        jd.autotune((5, 5, 5), device="cpu", iters=1)
+
+
+def test_autotune_picks_a_valid_process_grid():
+    run_ranks(_autotune_worker, 4)
+
+
+def test_init_finalize_are_idempotent():
+    jd.init()
+    jd.finalize()
+    jd.finalize()
+    x = torch.randn(4, 4, 4)
+    assert jd.pfft3d(x).shape == (4, 4, 4)
