@@ -31,6 +31,8 @@ from .plan import Step
 from .torch_backend import halo_regions
 
 _runtimes: Dict[tuple, "MeshRuntime"] = {}
+# switches that change how a plan is tiled: part of the plan key
+_TUNING_ENV = ("JD_B200_TILE_T", "JD_B200_BULK", "JD_B200_INTRAPAD", "JD_B200_ROWPAD", "JD_B200_FAST")
 
 
 def _stream() -> int:
@@ -56,6 +58,8 @@ class MeshRuntime:
         self.rt.set_timeout_ms(int(config.wait_timeout_ms))
         self.nat.trace_set_rank(mesh.rank)
         self._shapes: Dict[int, tuple] = {}
+        self._pycache: Dict[tuple, tuple] = {}
+        self.plan_hits = 0
 
     # ---- arena --------------------------------------------------------------------------------
     def ensure_arena(self, slot_bytes: int) -> None:
@@ -161,18 +165,21 @@ class MeshRuntime:
             raise ValueError("expected a 3-D block or a 4-D block with one leading batch dimension")
         nbatch = x.shape[0] if nb else 1
         lshape = tuple(x.shape[nb:])
-        if not _passes._group_steps(steps, self.mesh.pdims):
-            return x.clone()  # every step is an exchange over a single rank: the identity
-        key = "|".join(map(str, (steps, lshape, x.dtype, bool(inverse), float(scale), nbatch, self.mesh.pdims,
-                                  self.mesh.coords[-2:], os.environ.get("JD_B200_TILE_T", ""),
-                                  os.environ.get("JD_B200_BULK", ""), os.environ.get("JD_B200_INTRAPAD", ""),
-                                  os.environ.get("JD_B200_ROWPAD", ""), os.environ.get("JD_B200_FAST", ""))))
-        pid = self.rt.find_plan(key)
-        if pid < 0:
-            pid, final_shape = self.build_plan(key, steps, lshape, x.dtype, inverse, scale, nbatch)
-            self._shapes[pid] = final_shape
-        final_shape = self._shapes[pid]
-        need = self.rt.plan_slot_bytes(pid)
+        env = tuple(os.environ.get(k, "") for k in _TUNING_ENV)
+        pykey = (tuple(steps), lshape, x.dtype, bool(inverse), float(scale), nbatch, env)
+        hit = self._pycache.get(pykey)
+        if hit is None:
+            if not _passes._group_steps(steps, self.mesh.pdims):
+                return x.clone()  # every step is an exchange over a single rank: the identity
+            key = "|".join(map(str, pykey + (self.mesh.pdims, self.mesh.coords[-2:])))
+            pid = self.rt.find_plan(key)
+            if pid < 0:
+                pid, final_shape = self.build_plan(key, steps, lshape, x.dtype, inverse, scale, nbatch)
+                self._shapes[pid] = final_shape
+            hit = self._pycache[pykey] = (pid, self._shapes[pid], self.rt.plan_slot_bytes(pid))
+        else:
+            self.plan_hits += 1
+        pid, final_shape, need = hit
         if need > 0 or self.world > 1:
             self.ensure_arena(max(need, 1))
         out = torch.empty(((nbatch,) if nb else ()) + tuple(final_shape), dtype=x.dtype, device=x.device)

@@ -121,6 +121,29 @@ def test_lpt_step_native_vs_baseline_multi_gpu():
     run_ranks(_lpt_worker, world, backend="nccl", env={"NCCL_NVLS_ENABLE": "0"}, timeout=600)
 
 
+def _graph_worker(rank, world):
+    from jaxdecomp_b200.utils.graphs import capture
+
+    dev = torch.device("cuda", rank)
+    mesh = jd.make_mesh((1, world), ("z", "y"))
+    x = jd.ShardedTensor(torch.randn((32, 64 // world, 128), device=dev, dtype=torch.complex64), mesh)
+    g = capture(lambda v: jd.pifft3d(jd.pfft3d(v, backend="b200"), backend="b200"), x)
+    for seed in (1, 2, 3):
+        y = jd.ShardedTensor(torch.randn(x.local.shape, device=dev, dtype=torch.complex64,
+                                         generator=torch.Generator(device=dev).manual_seed(seed + rank)), mesh)
+        out = g(y)
+        torch.cuda.synchronize()
+        assert _rel(out.local, y.local) < 3e-5
+    from jaxdecomp_b200.ops import b200_backend
+
+    b200_backend.check_status(mesh, sync=True)
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs at least two GPUs")
+def test_cuda_graph_replay_across_ranks():
+    run_ranks(_graph_worker, 2, backend="nccl", env={"NCCL_NVLS_ENABLE": "0"}, timeout=300)
+
+
 def _barrier_worker(rank, world):
     from jaxdecomp_b200.ops import b200_backend
 

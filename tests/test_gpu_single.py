@@ -130,3 +130,14 @@ def test_large_offsets_use_64bit_indexing():
     assert abs(float(k.abs().max()) - 1.0) < 1e-4
     del k, x
     torch.cuda.empty_cache()
+
+
+def test_cuda_graph_capture_of_native_round_trip():
+    from jaxdecomp_b200.utils.graphs import capture
+
+    x = torch.randn((32, 64, 128), device=_dev(), dtype=torch.complex64)
+    g = capture(lambda v: jd.pifft3d(jd.pfft3d(v, backend="b200") * 2.0, backend="b200"), x)
+    for seed in (1, 2):
+        y = torch.randn((32, 64, 128), device=_dev(), dtype=torch.complex64, generator=torch.Generator(device=_dev()).manual_seed(seed))
+        out = g(y)
+        assert _rel(out, 2.0 * y) < 3e-5
