@@ -4,25 +4,33 @@
 // but every tile extent is a compile-time constant so that shared-memory
 // offsets become immediates, and the data path is shortened:
 //
-//   * stage 0 takes its eight inputs straight from global memory into
-//     registers (coalesced 8-byte loads along the pencil): no staging pass;
-//   * the butterflies of a pencil are owned by a fixed group of M/8 threads,
+//   * every thread owns sixteen values of one pencil, row[j + k*M/16]; a stage
+//     is a radix-16 butterfly on them or two radix-8 butterflies on interleaved
+//     halves, so lengths up to 4096 need at most three stages
+//     (128 = 16.8, 256 = 16.16, 512 = 8.8.8, 1024 = 16.8.8, 2048 = 16.16.8,
+//     4096 = 16.16.16) and therefore at most two shared-memory exchanges
+//     inside the transform -- profiles show the shared-memory data pipe, not
+//     HBM, to be the limiter of these passes;
+//   * stage 0 takes its inputs straight from global memory into registers
+//     (coalesced 8-byte loads along the pencil): no staging pass;
+//   * the butterflies of a pencil are owned by a fixed group of M/16 threads,
 //     which synchronise among themselves with a named barrier (or __syncwarp
-//     when the group is a warp) instead of a block-wide barrier;
-//   * twiddles come from per-stage tables laid out as eight consecutive
-//     factors per butterfly: four 16-byte loads, no multiplications to derive them;
+//     when the group fits in a warp) instead of a block-wide barrier;
+//   * per butterfly only the factors w, w^2, w^4 (w^8) are read from the table of
+//     M roots; the other powers are products of those (the FP pipe has head-room,
+//     the load pipe has not);
 //   * a plain (non-rotating) pass writes the last stage's results directly to
 //     global memory; a rotating pass goes through shared memory once more so
 //     that each thread stores 16 contiguous bytes along the destination's
-//     fastest axis, into the buffer of the peer that owns those columns.
-//
+//     fastest axis, into the buffer of the peer that owns those columns;
 //   * measured on B200, stores in runs shorter than 128 bytes reach only a
 //     fraction of the NVLink (64-byte runs: 479 of 715 GB/s) and HBM (64-byte
-//     runs: 3.2 of 6.2 TB/s) write bandwidth, so rotating passes use tiles of up
-//     to 16384 elements handled by up to 1024 threads, which doubles the length
-//     of every stored run (a thread-block-cluster variant that gathered the
-//     rows of neighbouring blocks through distributed shared memory was
-//     measured to be slower than single-block tiles and is not used).
+//     runs: 3.2 of 6.2 TB/s) write bandwidth, so passes whose stores cross
+//     NVLink use tiles of 16384 elements handled by up to 1024 threads, which
+//     doubles the length of every stored run (a thread-block-cluster variant
+//     that gathered the rows of neighbouring blocks through distributed shared
+//     memory, and a two-stage radix-32 variant with one warp per pencil, were
+//     both measured to be slower and are not used).
 //
 // Shared-memory rows use the padded layout of fft_core.h (padidx), which keeps
 // all exchange patterns free of bank conflicts for 8-byte elements.
@@ -35,44 +43,44 @@
 
 namespace jdb {
 
+// ---- stage plan ---------------------------------------------------------------------------------------------------
+// log2 of the radix of stage s for M = 2^logm (7 <= logm <= 12)
+__host__ __device__ constexpr int plan_radix_log(int logm, int s) {
+  switch (logm) {
+    case 7: return s == 0 ? 4 : 3;
+    case 8: return 4;
+    case 9: return 3;
+    case 10: return s == 0 ? 4 : 3;
+    case 11: return s < 2 ? 4 : 3;
+    default: return 4;  // 12
+  }
+}
+__host__ __device__ constexpr int plan_num_stages(int logm) { return logm <= 8 ? 2 : 3; }
+// log2 of Ls (length of the finished sub-transforms) before stage s
+__host__ __device__ constexpr int plan_log_ls(int logm, int s) {
+  int l = 0;
+  for (int i = 0; i < s; ++i) l += plan_radix_log(logm, i);
+  return l;
+}
 template <typename R, int LOGM_, int LOGT_, bool STORE_T_>
 struct FastCfg {
   static constexpr int LOGM = LOGM_, LOGT = LOGT_;
   static constexpr bool STORE_T = STORE_T_;
   static constexpr int M = 1 << LOGM, T = 1 << LOGT;
-  static constexpr int UPR = M / 8;            // butterflies (threads) per row
-  static constexpr int LOGUPR = LOGM - 3;
-  static constexpr int UNITS = T * UPR;
-  // two butterflies per thread once the tile is large enough; at most 1024 (complex64) / 512 (complex128) threads
-  static constexpr int NTMAX = sizeof(R) == 8 ? 512 : 1024;
-  static constexpr int NTWANT = UNITS >= 1024 ? UNITS / 2 : UNITS;
-  static constexpr int NT = NTWANT < NTMAX ? NTWANT : NTMAX;
-  static constexpr int ITERS = UNITS / NT;
+  static constexpr int UPR = M / 16;           // threads per row
+  static constexpr int LOGUPR = LOGM - 4;
+  static constexpr int NT = T * UPR;           // one thread owns 16 values of one row
   // threads that synchronise together: whole rows, and at most eight groups per block (named barriers 1..8)
   static constexpr int GS = UPR > NT / 8 ? UPR : NT / 8;
-  static constexpr int ROWS_PER_ROUND = NT / UPR;  // rows handled at once (>= 1 because UPR <= 512 <= ... see static_assert)
   static constexpr int ROWLEN = M + M / 8;
   static constexpr int PITCH = ROWLEN + 2;     // == 2 (mod 16): conflict-free transposed reads for 4 row pairs
-  static constexpr int N8 = LOGM / 3;
-  static constexpr int REM = LOGM - 3 * N8;    // log2 of the last, smaller radix (0 if none)
-  static constexpr int NS = N8 + (REM ? 1 : 0);
-  static constexpr int REGS = (sizeof(R) == 8 ? 2 : 1) * (ITERS <= 1 ? 40 : (ITERS == 2 ? 64 : 128));
+  static constexpr int NS = plan_num_stages(LOGM);
+  static constexpr int REGS = sizeof(R) == 8 ? 128 : 64;
   static constexpr int MINB_ = 65536 / (NT * REGS);
   static constexpr int MINB = MINB_ < 1 ? 1 : (MINB_ > 4 ? 4 : MINB_);
   static constexpr size_t SMEM = (size_t)T * PITCH * 2 * sizeof(R);
-  static_assert(NT % UPR == 0, "a row must be owned by whole thread groups");
-  static_assert(ITERS >= 1 && ITERS <= 4, "tile too large");
+  static_assert(NT >= 32 && NT <= 1024, "tile does not map onto one thread block");
 };
-
-// Per-stage twiddle table: for stage s >= 1 (Ls = 8^s) entry [off_s + kk*8 + q] = exp(-2 pi i q kk / (8 Ls)).
-__host__ __device__ constexpr int stage_table_offset(int s) {
-  int off = 0, ls = 8;
-  for (int i = 1; i < s; ++i) {
-    off += 8 * ls;
-    ls *= 8;
-  }
-  return off;
-}
 
 template <int UPR, int GS>
 __device__ __forceinline__ void group_sync(int sync_group) {
@@ -94,118 +102,164 @@ __device__ __forceinline__ cx<R> ldg_cx(const cx<R>* p) {
   }
 }
 
-template <typename R>
-__device__ __forceinline__ void load_tw8(const cx<R>* __restrict__ p, cx<R> w[8]) {
-  if constexpr (sizeof(R) == 4) {
-    const float4* q = reinterpret_cast<const float4*>(p);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float4 v = __ldg(q + i);
-      w[2 * i] = cx<R>{v.x, v.y};
-      w[2 * i + 1] = cx<R>{v.z, v.w};
-    }
-  } else {
-    const double2* q = reinterpret_cast<const double2*>(p);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const double2 v = __ldg(q + i);
-      w[i] = cx<R>{v.x, v.y};
-    }
+// a[FIRST + STRIDE*q] *= w^q for q = 1..N-1 (N = 8 or 16), where w^(2^i) are read from the table of M roots
+// (tw[n] = exp(-2 pi i n / M), `idx` = index of w) and the other powers are products of at most four of them.
+// The kernel is limited by the L1/shared-memory data pipe, so deriving twiddles on the FP pipe is cheaper
+// than loading a full row of factors per butterfly.
+template <typename R, int N, int FIRST, int STRIDE>
+__device__ __forceinline__ void apply_tw(const cx<R>* __restrict__ tw, int idx, cx<R> (&a)[16]) {
+  const cx<R> w1 = ldg_cx<R>(tw + idx), w2 = ldg_cx<R>(tw + 2 * idx), w4 = ldg_cx<R>(tw + 4 * idx);
+  const cx<R> w3 = cmul(w1, w2), w5 = cmul(w1, w4), w6 = cmul(w2, w4), w7 = cmul(w3, w4);
+  a[FIRST + STRIDE * 1] = cmul(a[FIRST + STRIDE * 1], w1);
+  a[FIRST + STRIDE * 2] = cmul(a[FIRST + STRIDE * 2], w2);
+  a[FIRST + STRIDE * 3] = cmul(a[FIRST + STRIDE * 3], w3);
+  a[FIRST + STRIDE * 4] = cmul(a[FIRST + STRIDE * 4], w4);
+  a[FIRST + STRIDE * 5] = cmul(a[FIRST + STRIDE * 5], w5);
+  a[FIRST + STRIDE * 6] = cmul(a[FIRST + STRIDE * 6], w6);
+  a[FIRST + STRIDE * 7] = cmul(a[FIRST + STRIDE * 7], w7);
+  if constexpr (N == 16) {
+    const cx<R> w8 = ldg_cx<R>(tw + 8 * idx);
+    a[FIRST + STRIDE * 8] = cmul(a[FIRST + STRIDE * 8], w8);
+    a[FIRST + STRIDE * 9] = cmul(a[FIRST + STRIDE * 9], cmul(w1, w8));
+    a[FIRST + STRIDE * 10] = cmul(a[FIRST + STRIDE * 10], cmul(w2, w8));
+    a[FIRST + STRIDE * 11] = cmul(a[FIRST + STRIDE * 11], cmul(w3, w8));
+    a[FIRST + STRIDE * 12] = cmul(a[FIRST + STRIDE * 12], cmul(w4, w8));
+    a[FIRST + STRIDE * 13] = cmul(a[FIRST + STRIDE * 13], cmul(w5, w8));
+    a[FIRST + STRIDE * 14] = cmul(a[FIRST + STRIDE * 14], cmul(w6, w8));
+    a[FIRST + STRIDE * 15] = cmul(a[FIRST + STRIDE * 15], cmul(w7, w8));
   }
 }
 
-template <typename Cfg, typename R, int S, int LOGLS>
-__device__ __forceinline__ void fast_stage(cx<R>* sm, const int (&rbase)[Cfg::ITERS], const int (&rowoff)[Cfg::ITERS], int j,
-                                           int sgroup, cx<R> (&a)[Cfg::ITERS][8], const cx<R>* __restrict__ tw,
-                                           const cx<R>* __restrict__ stw, bool to_smem) {
+// a * exp(-2 pi i K / 16), trivial cases resolved at compile time
+template <typename R, int K>
+__device__ __forceinline__ cx<R> mulw16(cx<R> a) {
+  constexpr int k = K & 15;
+  constexpr R c1 = (R)0.92387953251128673848, s1 = (R)0.38268343236508978178, h = (R)0.70710678118654752440;
+  if constexpr (k == 0) {
+    return a;
+  } else if constexpr (k == 4) {
+    return cx<R>{a.y, -a.x};
+  } else if constexpr (k == 8) {
+    return cx<R>{-a.x, -a.y};
+  } else if constexpr (k == 12) {
+    return cx<R>{-a.y, a.x};
+  } else if constexpr (k == 2) {
+    return cx<R>{(a.x + a.y) * h, (a.y - a.x) * h};
+  } else if constexpr (k == 6) {
+    return cx<R>{(a.y - a.x) * h, -(a.x + a.y) * h};
+  } else if constexpr (k == 10) {
+    return cx<R>{-(a.x + a.y) * h, (a.x - a.y) * h};
+  } else if constexpr (k == 14) {
+    return cx<R>{(a.x - a.y) * h, (a.x + a.y) * h};
+  } else {
+    // W = wr + i wi with wr = cos(pi k / 8), wi = -sin(pi k / 8)
+    constexpr R wr = (k == 1 || k == 15) ? c1 : (k == 3 || k == 13) ? s1 : (k == 5 || k == 11) ? -s1 : -c1;
+    constexpr R wi = (k == 1 || k == 7) ? -s1 : (k == 3 || k == 5) ? -c1 : (k == 9 || k == 15) ? s1 : c1;
+    return cx<R>{a.x * wr - a.y * wi, a.x * wi + a.y * wr};
+  }
+}
+
+// 16-point DFT in registers, natural order in and out (4 x 4 decomposition):
+// X[k1 + 4 k2] = sum_n W16^(n k1) W4^(n k2) sum_m x[n + 4 m] W4^(m k1)
+template <typename R>
+__device__ __forceinline__ void dft16(cx<R> (&a)[16]) {
+#pragma unroll
+  for (int n = 0; n < 4; ++n) dft4(a[n], a[n + 4], a[n + 8], a[n + 12]);  // a[n + 4 k1] = y_n[k1]
+  a[1 + 4] = mulw16<R, 1>(a[1 + 4]); a[1 + 8] = mulw16<R, 2>(a[1 + 8]); a[1 + 12] = mulw16<R, 3>(a[1 + 12]);
+  a[2 + 4] = mulw16<R, 2>(a[2 + 4]); a[2 + 8] = mulw16<R, 4>(a[2 + 8]); a[2 + 12] = mulw16<R, 6>(a[2 + 12]);
+  a[3 + 4] = mulw16<R, 3>(a[3 + 4]); a[3 + 8] = mulw16<R, 6>(a[3 + 8]); a[3 + 12] = mulw16<R, 9>(a[3 + 12]);
+  // second layer over n for each k1: inputs a[n + 4 k1], outputs X[k1 + 4 k2]
+  cx<R> t[16];
+#pragma unroll
+  for (int k1 = 0; k1 < 4; ++k1) {
+    cx<R> x0 = a[4 * k1], x1 = a[4 * k1 + 1], x2 = a[4 * k1 + 2], x3 = a[4 * k1 + 3];
+    dft4(x0, x1, x2, x3);
+    t[k1] = x0; t[k1 + 4] = x1; t[k1 + 8] = x2; t[k1 + 12] = x3;
+  }
+#pragma unroll
+  for (int k = 0; k < 16; ++k) a[k] = t[k];
+}
+
+// One stage on the sixteen values a[k] = row[j + k*M/16] of a thread.
+template <typename Cfg, typename R, int S>
+__device__ __forceinline__ void fast_stage(cx<R>* rowp, int j, int sgroup, cx<R> (&a)[16], const cx<R>* __restrict__ stw,
+                                           bool to_smem) {
   using E = cx<R>;
-  constexpr int M = Cfg::M, LOGM = Cfg::LOGM, ITERS = Cfg::ITERS;
-  constexpr int RL = S < Cfg::N8 ? 3 : Cfg::REM;
+  constexpr int LOGM = Cfg::LOGM;
+  constexpr int RL = plan_radix_log(LOGM, S);
+  constexpr int LOGLS = plan_log_ls(LOGM, S);
   constexpr int Ls = 1 << LOGLS;
-  constexpr int QP = Cfg::UPR + Cfg::UPR / 8;  // padded distance between a thread's eight inputs
+  constexpr int Q = Cfg::UPR;                  // distance between a thread's values
   if constexpr (S > 0) {
-    // inputs of this stage: the eight values at j + k*M/8 of the row
+    if constexpr (Q >= 16) {
+      constexpr int QP = Q + Q / 8;            // the padded distance is linear when Q is a multiple of 16
+      const E* p = rowp + padidx(j, 1);
 #pragma unroll
-    for (int it = 0; it < ITERS; ++it)
+      for (int k = 0; k < 16; ++k) a[k] = p[k * QP];
+    } else {
 #pragma unroll
-      for (int k = 0; k < 8; ++k) a[it][k] = sm[rbase[it] + k * QP];
+      for (int k = 0; k < 16; ++k) a[k] = rowp[padidx(j + k * Q, 1)];
+    }
     group_sync<Cfg::UPR, Cfg::GS>(sgroup);  // all reads of the group done before anyone overwrites
   }
-  if constexpr (RL == 3) {
+  if constexpr (RL == 4) {
     const int kk = j & (Ls - 1);
-    if constexpr (S > 0) {
-      E w[8];
-      load_tw8<R>(stw + stage_table_offset(S) + kk * 8, w);
-#pragma unroll
-      for (int it = 0; it < ITERS; ++it)
-#pragma unroll
-        for (int k = 1; k < 8; ++k) a[it][k] = cmul(a[it][k], w[k]);
-    }
-#pragma unroll
-    for (int it = 0; it < ITERS; ++it) dft8(a[it]);
+    if constexpr (S > 0) apply_tw<R, 16, 0, 1>(stw, kk << (LOGM - LOGLS - 4), a);
+    dft16<R>(a);
     if (to_smem) {
-      const int base = ((j - kk) << 3) + kk;
-      const int pb = padidx(base, 1);
+      const int base = ((j - kk) << 4) + kk;
+      if constexpr (LOGLS == 0) {
+        // sixteen consecutive columns: one padded group, eight 2-element vector stores
+        cx2<R>* v = reinterpret_cast<cx2<R>*>(rowp + padidx(base, 1));
 #pragma unroll
-      for (int it = 0; it < ITERS; ++it) {
-        E* p = sm + rowoff[it] + pb;
-        if constexpr (LOGLS == 0) {
-          cx2<R>* v = reinterpret_cast<cx2<R>*>(p);
+        for (int k = 0; k < 8; ++k) v[k] = cx2<R>{a[2 * k], a[2 * k + 1]};
+      } else {
+        // Ls >= 16 here (radix-16 stages come first): base + k*Ls stays linear in the padded layout
+        E* p = rowp + padidx(base, 1);
+        constexpr int LP = Ls + Ls / 8;
 #pragma unroll
-          for (int k = 0; k < 4; ++k) v[k] = cx2<R>{a[it][2 * k], a[it][2 * k + 1]};
-        } else if constexpr (LOGLS == 3) {
-#pragma unroll
-          for (int k = 0; k < 8; ++k) p[8 * k + 2 * (k >> 1)] = a[it][k];
-        } else {
-          constexpr int LP = Ls + Ls / 8;
-#pragma unroll
-          for (int k = 0; k < 8; ++k) p[k * LP] = a[it][k];
-        }
+        for (int k = 0; k < 16; ++k) p[k * LP] = a[k];
       }
     }
-  } else if constexpr (RL == 2) {
-    // two radix-4 butterflies b = j + m*M/8 on (a[m], a[m+2], a[m+4], a[m+6]); Ls == M/4
+  } else {
+    // two radix-8 butterflies b = j + m*M/16 on the values k = m + 2q
 #pragma unroll
     for (int m = 0; m < 2; ++m) {
-      const int bfly = j + m * Cfg::UPR;
-      const E w1 = ldg_cx<R>(tw + bfly), w2 = ldg_cx<R>(tw + 2 * bfly);
-      const E w3 = cmul(w1, w2);
-#pragma unroll
-      for (int it = 0; it < ITERS; ++it) {
-        E x0 = a[it][m], x1 = cmul(a[it][m + 2], w1), x2 = cmul(a[it][m + 4], w2), x3 = cmul(a[it][m + 6], w3);
-        dft4(x0, x1, x2, x3);
-        a[it][m] = x0; a[it][m + 2] = x1; a[it][m + 4] = x2; a[it][m + 6] = x3;
+      const int bf = j + m * Q;
+      const int kk = bf & (Ls - 1);
+      if constexpr (S > 0) {
+        if (m == 0) apply_tw<R, 8, 0, 2>(stw, kk << (LOGM - LOGLS - 3), a);
+        else apply_tw<R, 8, 1, 2>(stw, kk << (LOGM - LOGLS - 3), a);
       }
-    }
-    if (to_smem) {
+      E x[8];
 #pragma unroll
-      for (int it = 0; it < ITERS; ++it)
+      for (int q = 0; q < 8; ++q) x[q] = a[m + 2 * q];
+      dft8(x);
+      if (to_smem) {
+        const int base = ((bf - kk) << 3) + kk;
+        if constexpr (LOGLS == 0) {
+          cx2<R>* v = reinterpret_cast<cx2<R>*>(rowp + padidx(base, 1));
 #pragma unroll
-        for (int k = 0; k < 8; ++k) sm[rbase[it] + k * QP] = a[it][k];  // output b + q*M/4 == j + (m + 2q)*M/8
-    }
-  } else if constexpr (RL == 1) {
-    // four radix-2 butterflies b = j + m*M/8 on (a[m], a[m+4]); Ls == M/2
+          for (int q = 0; q < 4; ++q) v[q] = cx2<R>{x[2 * q], x[2 * q + 1]};
+        } else if constexpr (LOGLS == 3) {
+          E* p = rowp + padidx(base, 1);
 #pragma unroll
-    for (int m = 0; m < 4; ++m) {
-      const E w = ldg_cx<R>(tw + j + m * Cfg::UPR);
+          for (int q = 0; q < 8; ++q) p[8 * q + 2 * (q >> 1)] = x[q];
+        } else {
+          E* p = rowp + padidx(base, 1);
+          constexpr int LP = Ls + Ls / 8;
 #pragma unroll
-      for (int it = 0; it < ITERS; ++it) {
-        E x0 = a[it][m], x1 = cmul(a[it][m + 4], w);
-        dft2(x0, x1);
-        a[it][m] = x0;
-        a[it][m + 4] = x1;
+          for (int q = 0; q < 8; ++q) p[q * LP] = x[q];
+        }
+      } else {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) a[m + 2 * q] = x[q];
       }
-    }
-    if (to_smem) {
-#pragma unroll
-      for (int it = 0; it < ITERS; ++it)
-#pragma unroll
-        for (int k = 0; k < 8; ++k) sm[rbase[it] + k * QP] = a[it][k];
     }
   }
   if constexpr (S + 1 < Cfg::NS) {
     group_sync<Cfg::UPR, Cfg::GS>(sgroup);  // this stage's writes visible to the group
-    fast_stage<Cfg, R, S + 1, LOGLS + RL>(sm, rbase, rowoff, j, sgroup, a, tw, stw, (S + 2 < Cfg::NS) || Cfg::STORE_T);
+    fast_stage<Cfg, R, S + 1>(rowp, j, sgroup, a, stw, (S + 2 < Cfg::NS) || Cfg::STORE_T);
   }
 }
 
@@ -214,7 +268,7 @@ __global__ void __launch_bounds__((FastCfg<R, LOGM, LOGT, STORE_T>::NT), (FastCf
     fft_fast_kernel(const __grid_constant__ PassDesc d) {
   using Cfg = FastCfg<R, LOGM, LOGT, STORE_T>;
   using E = cx<R>;
-  constexpr int M = Cfg::M, T = Cfg::T, NT = Cfg::NT, ITERS = Cfg::ITERS, UPR = Cfg::UPR;
+  constexpr int M = Cfg::M, T = Cfg::T, NT = Cfg::NT, UPR = Cfg::UPR;
   extern __shared__ __align__(16) unsigned char fast_smem[];
   E* sm = reinterpret_cast<E*>(fast_smem);
 
@@ -227,50 +281,38 @@ __global__ void __launch_bounds__((FastCfg<R, LOGM, LOGT, STORE_T>::NT), (FastCf
   const bool inv = d.inverse != 0;
 
   const int j = tid & (UPR - 1);
-  const int group = tid >> Cfg::LOGUPR;
-  int rbase[ITERS], rowoff[ITERS];
-  E a[ITERS][8];
-  const E* __restrict__ in = (const E*)d.in + ((long long)o * d.is_o + (long long)b * d.is_b + (long long)t0 * d.is_t);
+  const int row = tid >> Cfg::LOGUPR;
+  E* rowp = sm + row * Cfg::PITCH;
+  E a[16];
+  {
+    const E* __restrict__ src =
+        (const E*)d.in + ((long long)o * d.is_o + (long long)b * d.is_b + (long long)(t0 + row) * d.is_t + j);
 #pragma unroll
-  for (int it = 0; it < ITERS; ++it) {
-    const int row = it * Cfg::ROWS_PER_ROUND + group;
-    rowoff[it] = row * Cfg::PITCH;
-    rbase[it] = rowoff[it] + padidx(j, 1);
-    const E* src = in + (long long)row * d.is_t + j;
-#pragma unroll
-    for (int k = 0; k < 8; ++k) a[it][k] = src[k * UPR];
+    for (int k = 0; k < 16; ++k) a[k] = src[k * UPR];
   }
   if (inv) {
 #pragma unroll
-    for (int it = 0; it < ITERS; ++it)
-#pragma unroll
-      for (int k = 0; k < 8; ++k) a[it][k] = cswap(a[it][k]);
+    for (int k = 0; k < 16; ++k) a[k] = cswap(a[k]);
   }
-  const E* __restrict__ tw = (const E*)d.twiddle;
-  const E* __restrict__ stw = (const E*)d.bhat;  // per-stage twiddle table travels in the (otherwise unused) bhat slot
-  fast_stage<Cfg, R, 0, 0>(sm, rbase, rowoff, j, tid / Cfg::GS, a, tw, stw, Cfg::NS > 1 || STORE_T);
+  const E* __restrict__ stw = (const E*)d.twiddle;  // M roots of unity
+  fast_stage<Cfg, R, 0>(rowp, j, tid / Cfg::GS, a, stw, Cfg::NS > 1 || STORE_T);
 
   const R scale = (R)d.scale;
   const bool do_scale = d.scale != 1.0;
   if constexpr (!STORE_T) {
-    // results of the last stage sit in registers in natural order positions:
-    // radix 8: j + k*M/8 holds output index base + k*Ls with Ls == M/8  -> column j + k*M/8
-    // radix 4/2: same columns (see fast_stage).  Store them straight to global memory.
+    // After the last stage a[k] is the result for column j + k*M/16: store straight to global memory.
     const OutBase ob = out_base_for(d, o, b);
+    const int t = t0 + row;
+    const int pt = d.split_axis == 2 ? t / d.Tl : 0;
+    const long long toff = ob.off + (long long)(t - pt * d.Tl) * d.os_t;
 #pragma unroll
-    for (int it = 0; it < ITERS; ++it) {
-      const int t = t0 + it * Cfg::ROWS_PER_ROUND + group;
-      const int pt = d.split_axis == 2 ? t / d.Tl : 0;
-      const long long toff = ob.off + (long long)(t - pt * d.Tl) * d.os_t;
-#pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        const int c = j + k * UPR;
-        E v = a[it][k];
-        if (inv) v = cswap(v);
-        if (do_scale) v = cscale(v, scale);
-        const int pc = d.split_axis == 1 ? c / d.Cl : 0;
-        ((E*)d.out[ob.peer + pc + pt])[toff + (c - pc * d.Cl)] = v;
-      }
+    for (int k = 0; k < 16; ++k) {
+      const int c = j + k * UPR;
+      E v = a[k];
+      if (inv) v = cswap(v);
+      if (do_scale) v = cscale(v, scale);
+      const int pc = d.split_axis == 1 ? c / d.Cl : 0;
+      ((E*)d.out[ob.peer + pc + pt])[toff + (c - pc * d.Cl)] = v;
     }
   } else {
     __syncthreads();  // the transposed store reads every row of the tile
@@ -316,7 +358,6 @@ __global__ void __launch_bounds__((FastCfg<R, LOGM, LOGT, STORE_T>::NT), (FastCf
 // ---- host side --------------------------------------------------------------------------------------------------
 static bool is_pow2(long long v) { return v > 0 && (v & (v - 1)) == 0; }
 
-// The tile height the fast kernel is instantiated with for a given length and element size.
 static bool big_tiles(const PassDesc& d) {
   // Large tiles (128 KiB of data, one block per SM) double the stored run length of rotating
   // passes.  Measured: they pay off when the stores cross NVLink (128-byte runs reach the full
@@ -340,14 +381,13 @@ int fast_pass_logT(int logM, int elem_bytes, bool big) {
 bool fast_pass_eligible(const PassDesc& d) {
   if (d.fft_mode != JD_FFT_POW2) return false;
   if (d.elem_bytes != 8 && d.elem_bytes != 16) return false;
-  if (d.M < 128 || d.M > (d.elem_bytes == 8 ? 4096 : 2048) || d.C != d.M) return false;
+  if (d.M < (d.elem_bytes == 8 ? 128 : 256) || d.M > (d.elem_bytes == 8 ? 4096 : 2048) || d.C != d.M) return false;
   if (d.load_t_contig || d.is_c != 1) return false;
   int logM = 0;
   while ((1 << logM) < d.M) ++logM;
   // the small tile height must divide the rows (the big variant is used only when it divides too)
   const int lt = fast_pass_logT(logM, d.elem_bytes, false);
   if (d.Tn % (1 << lt)) return false;
-  if (!d.bhat) return false;  // per-stage twiddle table
   if (d.store_t_contig) {
     if (d.os_t != 1) return false;
     const int per16 = 16 / d.elem_bytes;
@@ -416,7 +456,9 @@ static int launch_fast_m(const PassDesc& d, cudaStream_t stream) {
 template <typename R>
 static int launch_fast_r(const PassDesc& d, cudaStream_t stream) {
   switch (d.M) {
-    case 128: return launch_fast_m<R, 7>(d, stream);
+    case 128:
+      if constexpr (sizeof(R) == 4) return launch_fast_m<R, 7>(d, stream);
+      return JD_ERR_UNSUPPORTED;
     case 256: return launch_fast_m<R, 8>(d, stream);
     case 512: return launch_fast_m<R, 9>(d, stream);
     case 1024: return launch_fast_m<R, 10>(d, stream);

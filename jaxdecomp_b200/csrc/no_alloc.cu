@@ -97,7 +97,6 @@ PassDesc make_pass(int A, int B, int C, int rotate, const float2* tw, int invers
   d.Cc = C;
   d.pitch = C + 2;
   d.twiddle = tw;
-  // bhat stays null: selects the general kernel, which needs no per-stage tables
   return d;
 }
 

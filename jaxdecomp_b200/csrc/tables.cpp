@@ -100,25 +100,6 @@ FftTables get_fft_tables(int C, int M, int elem_bytes, bool device) {
       tw[n] = cld(cosl(ang), sinl(ang));
     }
     ts.twiddle = upload(tw, elem_bytes, device);
-    if (C == M) {
-      // per-stage twiddles for the specialised kernel: for every radix-8 stage s >= 1
-      // (Ls = 8^s) and every kk < Ls, eight consecutive factors exp(-2 pi i q kk / (8 Ls))
-      int logM = 0;
-      while ((1 << logM) < M) ++logM;
-      const int n8 = logM / 3;
-      std::vector<cld> st;
-      long long ls = 8;
-      for (int s2 = 1; s2 < n8; ++s2) {
-        for (long long kk = 0; kk < ls; ++kk)
-          for (int q = 0; q < 8; ++q) {
-            const long double ang = -2.0L * kPi * (long double)(q * kk) / (long double)(8 * ls);
-            st.push_back(cld(cosl(ang), sinl(ang)));
-          }
-        ls *= 8;
-      }
-      if (st.empty()) st.assign(8, cld(1, 0));
-      ts.bhat = upload(st, elem_bytes, device);
-    }
     if (C != M) {
       if (M < 2 * C - 1) throw std::runtime_error("tables: Bluestein length too short");
       std::vector<cld> chirp(C), b(M, cld(0, 0));
