@@ -18,7 +18,7 @@ aliases so that code written against the reference runs unchanged.
 from __future__ import annotations
 
 from .ops.fft import fftfreq3d, pfft3d, pifft3d, rfftfreq3d
-from .ops.halo import halo_accumulate, halo_exchange, halo_reduce, pad_halo, unpad_halo
+from .ops.halo import halo_accumulate, halo_exchange, halo_exchange_, halo_reduce, pad_halo, unpad_halo
 from .ops.transpose import (
     transpose_shard,
     transposeXtoY,
@@ -86,7 +86,7 @@ __version__ = "0.1.0"
 
 __all__ = [
     "config", "init", "finalize", "get_pencil_info", "get_autotuned_config", "make_config", "autotune",
-    "halo_exchange", "halo_accumulate", "halo_reduce", "pad_halo", "unpad_halo",
+    "halo_exchange", "halo_exchange_", "halo_accumulate", "halo_reduce", "pad_halo", "unpad_halo",
     "pfft3d", "pifft3d", "fftfreq3d", "rfftfreq3d",
     "transposeXtoY", "transposeYtoX", "transposeYtoZ", "transposeZtoY", "transposeXtoZ", "transposeZtoX",
     "transpose_shard",

@@ -210,13 +210,22 @@ class MeshRuntime:
     def _arena_rank(self, rank):
         return -1 if rank is None else self.ranks.index(rank)
 
-    def halo_exchange(self, x: torch.Tensor, extents, periods) -> torch.Tensor:
-        x = _aligned(x)
+    def halo_exchange(self, x: torch.Tensor, extents, periods, inplace: bool = False) -> torch.Tensor:
+        if inplace:
+            if not x.is_contiguous() or x.data_ptr() % 16:
+                raise ValueError("in-place halo exchange needs a contiguous, 16-byte aligned block")
+        else:
+            x = _aligned(x)
         nb, B, (S0, S1, S2), regions, offs, total = self._halo_common(x, extents, periods)
-        out = torch.empty_like(x)
-        if not regions:
-            out.copy_(x)
-            return out
+        if inplace:
+            out = x
+            if not regions:
+                return out
+        else:
+            out = torch.empty_like(x)
+            if not regions:
+                out.copy_(x)
+                return out
         eb = x.element_size()
         per = (bool(periods[0]), bool(periods[1]))
         pack, unpack = [], []
@@ -267,8 +276,8 @@ def run_steps(x: torch.Tensor, steps: Sequence[Step], mesh: Mesh, inverse: bool,
     return get_runtime(mesh).run_steps(x, steps, inverse, scale)
 
 
-def halo_exchange(x, extents, periods, mesh: Mesh) -> torch.Tensor:
-    return get_runtime(mesh).halo_exchange(x, extents, periods)
+def halo_exchange(x, extents, periods, mesh: Mesh, inplace: bool = False) -> torch.Tensor:
+    return get_runtime(mesh).halo_exchange(x, extents, periods, inplace=inplace)
 
 
 def halo_accumulate(g, extents, periods, mesh: Mesh) -> torch.Tensor:

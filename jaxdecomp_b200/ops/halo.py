@@ -115,6 +115,26 @@ def halo_exchange(x, halo_extents: Sequence[int], halo_periods: Sequence[bool], 
     return y if plain else ShardedTensor(y, st.mesh, st.spec)
 
 
+def halo_exchange_(x, halo_extents: Sequence[int], halo_periods: Sequence[bool], backend: str = "auto"):
+    """In-place variant of :func:`halo_exchange`: overwrites the halo regions of ``x`` and returns it.
+    Not differentiable (use the functional op under autograd).  On the native backend this skips the
+    copy of the padded block, so only the face and corner slabs move."""
+    extents, periods = _check(halo_extents, halo_periods)
+    st, plain = as_sharded(x)
+    if st.local.requires_grad and torch.is_grad_enabled():
+        raise RuntimeError("halo_exchange_ is not differentiable; use halo_exchange")
+    b = resolve_backend(backend, st.local, family="halo")
+    if b == "b200":
+        from . import b200_backend
+
+        b200_backend.halo_exchange(st.local, extents, periods, st.mesh, inplace=True)
+    else:
+        from . import torch_backend
+
+        st.local.copy_(torch_backend.halo_exchange(st.local, extents, periods, st.mesh))
+    return x
+
+
 def halo_accumulate(x, halo_extents: Sequence[int], halo_periods: Sequence[bool], backend: str = "auto"):
     """Add the content of every halo region into the interior edge of the rank
     that owns those cells, and zero the halos (adjoint of :func:`halo_exchange`)."""

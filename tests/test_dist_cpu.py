@@ -145,6 +145,7 @@ def _halo_worker(rank, world, pdims, periods):
     out = jd.halo_exchange(st, h, periods)
     want = _expected_halo(blocks, pdims, tuple(mesh.coords), h, periods)
     assert torch.equal(out.local, want)
+    assert torch.equal(jd.halo_exchange_(jd.ShardedTensor(mine.clone(), mesh), h, periods).local, want)
     # exact adjoint: <L x, y> == <x, L^T y> summed over ranks
     y = torch.randn(mine.shape, generator=torch.Generator().manual_seed(100 + rank))
     lty = jd.halo_accumulate(jd.ShardedTensor(y, mesh), h, periods)

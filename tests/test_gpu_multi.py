@@ -66,6 +66,8 @@ def _ops_worker(rank, world):
                 a = jd.halo_exchange(st, (2, 3), periods, backend="b200")
                 b = jd.halo_exchange(st, (2, 3), periods, backend="torch")
                 assert torch.equal(a.local, b.local), (pdims, periods)
+                c = jd.halo_exchange_(jd.ShardedTensor(blk.clone(), mesh), (2, 3), periods, backend="b200")
+                assert torch.equal(c.local, b.local), (pdims, periods)
                 a = jd.halo_accumulate(st, (2, 3), periods, backend="b200")
                 b = jd.halo_accumulate(st, (2, 3), periods, backend="torch")
                 torch.testing.assert_close(a.local, b.local, rtol=1e-6, atol=1e-6)
