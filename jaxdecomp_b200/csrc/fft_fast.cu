@@ -322,9 +322,18 @@ __global__ void __launch_bounds__((FastCfg<R, LOGM, LOGT, STORE_T>::NT), (FastCf
     constexpr int STEP = NT / TP;                    // columns advanced per iteration
     static_assert(STEP % 16 == 0, "column step must keep the padded index linear");
     constexpr int STEPP = STEP + STEP / 8;
-    const int tp = tid & (TP - 1);
+    // Thread -> (row pair tp, column cs).  Sixteen consecutive threads always cover four row pairs x
+    // four columns: with PITCH == 2 (mod 16) their 8-byte reads then fall into sixteen different banks.
+    int tp, cs;
+    if constexpr (TP >= 8) {
+      const int rest = tid >> 4;
+      tp = (tid & 3) + 4 * (rest & (TP / 4 - 1));
+      cs = ((tid >> 2) & 3) + 4 * (rest / (TP / 4));
+    } else {
+      tp = tid & (TP - 1);
+      cs = tid >> LOGTP;
+    }
     const int t = tp * PER16;
-    const int cs = tid >> LOGTP;
     const OutBase ob = out_base_for(d, o, b);
     const int tg = t0 + t;
     const int pt = d.split_axis == 2 ? tg / d.Tl : 0;
@@ -364,7 +373,9 @@ static bool big_tiles(const PassDesc& d) {
   // peer-store bandwidth) and lose slightly for local passes, so they are the default only there.
   const char* env = std::getenv("JD_B200_BIGTILE");
   if (env && *env) return env[0] != '0';
-  return d.store_t_contig != 0 && d.npeers > 1;
+  if (!d.store_t_contig) return false;
+  // local rotating passes: measured 3 % faster with large tiles at 1024 points, slower at 512 and below
+  return d.npeers > 1 || d.M == 1024;
 }
 
 int fast_pass_logT(int logM, int elem_bytes, bool big) {
