@@ -70,6 +70,7 @@ def main():
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--lpt-size", type=int, default=None)
+    ap.add_argument("--graph", action="store_true", help="also time pfft3d+pifft3d replayed from a CUDA graph")
     ap.add_argument("--local-shape", type=int, nargs=3, default=None,
                     help="local X-pencil block per GPU (weak scaling, e.g. 64 128 128); overrides --size for fft/transpose")
     args = ap.parse_args()
@@ -116,6 +117,15 @@ def main():
                 emit(op=name, backend=backend, ms=ms, gflops=flops / ms / 1e6, roofline_ms=max(t_link, t_hbm),
                      roofline_bound="nvlink" if t_link > t_hbm else "hbm", frac_of_roofline=max(t_link, t_hbm) / ms,
                      peaks=f"hbm {hbm:.0f} GB/s ({hbm_src}), nvlink {NVLINK_GBS:.0f} GB/s per direction (measured peer copy)")
+            if args.graph and backend == "b200":
+                from jaxdecomp_b200.utils.graphs import capture
+
+                g = capture(lambda v: jd.pifft3d(jd.pfft3d(v, backend="b200"), backend="b200"), x)
+                ms = timed(lambda: g.graph.replay(), args.warmup, max(args.iters, 50), world, device)
+                emit(op="pfft3d+pifft3d (CUDA graph replay)", backend=backend, ms=ms, gflops=2 * flops / ms / 1e6)
+                ms = timed(lambda: jd.pifft3d(jd.pfft3d(x, backend="b200"), backend="b200"), args.warmup,
+                           max(args.iters, 50), world, device)
+                emit(op="pfft3d+pifft3d (eager)", backend=backend, ms=ms, gflops=2 * flops / ms / 1e6)
             del k
         if "transpose" in ops:
             x = jd.ShardedTensor(torch.randn(lshape, generator=gen, device=device, dtype=rdt).to(cdt), mesh)

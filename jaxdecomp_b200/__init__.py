@@ -45,7 +45,10 @@ from .utils.api import (
     autotune,
     finalize,
     get_autotuned_config,
+    get_fft_workspace_size,
+    get_halo_workspace_size,
     get_pencil_info,
+    get_transpose_workspace_size,
     init,
     make_config,
 )
@@ -86,6 +89,7 @@ __version__ = "0.1.0"
 
 __all__ = [
     "config", "init", "finalize", "get_pencil_info", "get_autotuned_config", "make_config", "autotune",
+    "get_fft_workspace_size", "get_transpose_workspace_size", "get_halo_workspace_size",
     "halo_exchange", "halo_exchange_", "halo_accumulate", "halo_reduce", "pad_halo", "unpad_halo",
     "pfft3d", "pifft3d", "fftfreq3d", "rfftfreq3d",
     "transposeXtoY", "transposeYtoX", "transposeYtoZ", "transposeZtoY", "transposeXtoZ", "transposeZtoX",

@@ -258,9 +258,25 @@ def choose_tiling(spec: PassSpec, elem_bytes: int, remote: bool) -> dict:
     return out
 
 
+def check_pass_bounds(spec: PassSpec) -> None:
+    """Index-range check done once, when a plan is built: the largest element offset a pass can read
+    or write must stay inside the dense block of ``numel`` elements on either side.  (The kernels
+    themselves carry no per-access checks; every address they form is one of the offsets bounded here.)"""
+    ext = spec.ext
+    hi_in = sum((e - 1) * s for e, s in zip(ext, spec.in_strides))
+    hi_out = spec.out_base + sum((c - 1) * s for c, s in zip(spec.chunks, spec.out_strides))
+    lo_out = spec.out_base
+    if hi_in >= spec.numel or lo_out < 0 or hi_out >= spec.numel:
+        raise AssertionError(
+            f"tile pass addresses leave the block: max input offset {hi_in}, output offsets [{lo_out}, {hi_out}], "
+            f"block of {spec.numel} elements ({spec})"
+        )
+
+
 def fill_desc(native, spec: PassSpec, elem_bytes: int, inverse: bool, scale: float, batch: int,
               remote: bool, device_tables: bool):
     """Build a native ``PassDesc`` (addresses left empty) for a pass."""
+    check_pass_bounds(spec)
     d = native.PassDesc()
     C, Tn, On = spec.ext
     d.C, d.Tn, d.On, d.B = C, Tn, On, int(batch)

@@ -189,3 +189,33 @@ def get_autotuned_config(grid_config: GridConfig, double_precision: bool = False
     return GridConfig(tuple(grid_config.gdims), tuple(best[0]),
                       TRANSPOSE_COMM_P2P if native else TRANSPOSE_COMM_NCCL,
                       HALO_COMM_P2P if native else HALO_COMM_NCCL)
+
+
+def _workspace_bytes(gdims, pdims, elem_bytes: int, slots: int) -> int:
+    n0, n1, n2 = (int(g) for g in gdims)
+    p0, p1 = (int(p) for p in pdims)
+    local = (n0 // p0) * (n1 // p1) * n2
+    return slots * local * int(elem_bytes)
+
+
+def get_fft_workspace_size(grid_config: GridConfig, double_precision: bool = False) -> int:
+    """Bytes of peer-visible arena a distributed FFT of this grid needs on each rank (two pencil
+    buffers; one on a single rank).  Counterpart of the reference's workspace query
+    (``src/csrc/jaxdecomp.cc:400-427``); the arena is sized automatically, this is informational."""
+    single = tuple(grid_config.pdims) == (1, 1)
+    return _workspace_bytes(grid_config.gdims, grid_config.pdims, 16 if double_precision else 8, 1 if single else 2)
+
+
+def get_transpose_workspace_size(grid_config: GridConfig, elem_bytes: int = 8) -> int:
+    """Bytes of arena used by a stand-alone transpose (one pencil buffer)."""
+    return _workspace_bytes(grid_config.gdims, grid_config.pdims, elem_bytes, 1)
+
+
+def get_halo_workspace_size(grid_config: GridConfig, halo_extents: Sequence[int], elem_bytes: int = 4) -> int:
+    """Bytes of arena staging used by a halo exchange of the padded X-pencil block."""
+    n0, n1, n2 = (int(g) for g in grid_config.gdims)
+    p0, p1 = (int(p) for p in grid_config.pdims)
+    h0 = int(halo_extents[0]) if p0 > 1 else 0
+    h1 = int(halo_extents[1]) if p1 > 1 else 0
+    s0, s1 = n0 // p0 + 2 * h0, n1 // p1 + 2 * h1
+    return (2 * h0 * s1 + 2 * h1 * s0 - 4 * h0 * h1) * n2 * int(elem_bytes)

@@ -146,6 +146,27 @@ def test_cuda_graph_replay_across_ranks():
     run_ranks(_graph_worker, 2, backend="nccl", env={"NCCL_NVLS_ENABLE": "0"}, timeout=300)
 
 
+def _autotune_worker(rank, world):
+    best, timings = jd.autotune((64, 64, 64), dtype=torch.complex64, iters=2, return_timings=True)
+    assert best in timings and all(t > 0 for t in timings.values())
+    cfg = jd.get_autotuned_config(jd.make_config((64, 64, 64), (1, world)), False, True, True, False, (2, 2, 0),
+                                  (True, True, True))
+    assert cfg.pdims in timings
+    # complex halos on the native path
+    mesh = jd.make_mesh((1, world), ("z", "y"))
+    blk = torch.randn((8, 12, 6), device=torch.device("cuda", rank), dtype=torch.complex128)
+    st = jd.ShardedTensor(blk, mesh)
+    assert torch.equal(jd.halo_exchange(st, (0, 2), (True, True), backend="b200").local,
+                       jd.halo_exchange(st, (0, 2), (True, True), backend="torch").local)
+    torch.testing.assert_close(jd.halo_accumulate(st, (0, 2), (True, False), backend="b200").local,
+                               jd.halo_accumulate(st, (0, 2), (True, False), backend="torch").local)
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs at least two GPUs")
+def test_autotune_and_complex_halos_on_gpus():
+    run_ranks(_autotune_worker, 2, backend="nccl", env={"NCCL_NVLS_ENABLE": "0"}, timeout=300)
+
+
 def _barrier_worker(rank, world):
     from jaxdecomp_b200.ops import b200_backend
 

@@ -158,3 +158,19 @@ def test_single_rank_plain_tensor_api():
         from jaxdecomp_b200.ops.fft import prfft3d
 
         prfft3d(x)
+
+
+def test_workspace_queries_and_bounds_check():
+    cfg = jd.make_config((1024, 1024, 1024), (2, 4))
+    assert jd.get_fft_workspace_size(cfg) == 2 * (1 << 30)
+    assert jd.get_fft_workspace_size(jd.make_config((64, 64, 64), (1, 1)), True) == 64 ** 3 * 16
+    assert jd.get_transpose_workspace_size(cfg, 4) == (1 << 30) // 2
+    assert jd.get_halo_workspace_size(cfg, (16, 16)) == (2 * 16 * 288 + 2 * 16 * 544 - 4 * 256) * 1024 * 4
+    steps = plan.fft_steps(jd.PENCILS, False, True, native=True)
+    specs, _ = passes.compile_passes(steps, (4, 4, 32), (2, 4), (1, 3))
+    for sp in specs:
+        passes.check_pass_bounds(sp)
+    bad = specs[0]
+    bad.out_base += bad.numel
+    with pytest.raises(AssertionError):
+        passes.check_pass_bounds(bad)
