@@ -59,6 +59,7 @@ PYBIND11_MODULE(_jdb200, m) {
   m.attr("COPY") = (int)JD_COPY;
   m.attr("FFT_POW2") = (int)JD_FFT_POW2;
   m.attr("FFT_BLUESTEIN") = (int)JD_FFT_BLUESTEIN;
+  m.attr("FFT_MIXED") = (int)JD_FFT_MIXED;
   m.attr("BUF_USER_IN") = (int)BUF_USER_IN;
   m.attr("BUF_USER_OUT") = (int)BUF_USER_OUT;
   m.attr("BUF_SLOT_A") = (int)BUF_SLOT_A;

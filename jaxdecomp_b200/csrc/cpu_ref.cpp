@@ -7,6 +7,7 @@
 #include <cstring>
 #include <vector>
 
+#include "fft_mixed.h"
 #include "launch.h"
 #include "tile_ops.h"  // also brings fft_core.h
 
@@ -34,9 +35,55 @@ static void fft_rows_host(const PassDesc& d, E* tile) {
   }
 }
 
+template <typename R>
+struct HostStage {
+  const MixedStage& st;
+  const cx<R>* tw;
+  const cx<R>* src;
+  cx<R>* dst;
+  template <int RADIX>
+  void run() {
+    mixed_stage_row<R, RADIX>(st, tw, src, dst, 0, 1);
+  }
+};
+
+// Mixed-radix rows: ping-pong between `tile` and `other`; returns the buffer that holds the result.
+template <typename E>
+static E* mixed_rows_host(const PassDesc& d, const MixedPlan& pl, E* tile, E* other) {
+  if constexpr (elem_traits<E>::is_complex) {
+    using R = typename elem_traits<E>::real;
+    for (int s = 0; s < pl.ns; ++s) {
+      for (int r = 0; r < d.T; ++r) {
+        HostStage<R> hs{pl.st[s], (const E*)d.twiddle, tile + (long long)r * d.pitch, other + (long long)r * d.pitch};
+        mixed_dispatch(pl.st[s].radix, hs);
+      }
+      E* tmp = tile;
+      tile = other;
+      other = tmp;
+    }
+  }
+  return tile;
+}
+
 template <typename E>
 static int run_pass_host_t(const PassDesc& d) {
   const bool fft = d.fft_mode != JD_COPY;
+  if (d.fft_mode == JD_FFT_MIXED) {
+    MixedPlan pl;
+    if (!make_mixed_plan(d.M, &pl)) return JD_ERR_INVALID_ARG;
+    const int tiles = (d.Tn + d.T - 1) / d.T;
+    std::vector<E> bufa((size_t)d.T * d.pitch), bufb((size_t)d.T * d.pitch);
+    const int NT = 64;
+    for (int b = 0; b < d.B; ++b)
+      for (int o = 0; o < d.On; ++o)
+        for (int tt = 0; tt < tiles; ++tt) {
+          const int t0 = tt * d.T;
+          for (int tid = 0; tid < NT; ++tid) tile_load<E>(d, bufa.data(), o, t0, 0, b, tid, NT);
+          const E* res = mixed_rows_host<E>(d, pl, bufa.data(), bufb.data());
+          for (int tid = 0; tid < NT; ++tid) tile_store<E>(d, res, o, t0, 0, b, tid, NT);
+        }
+    return JD_OK;
+  }
   const int tiles_t = (d.Tn + d.T - 1) / d.T;
   const int tiles_c = fft ? 1 : (d.C + d.Cc - 1) / d.Cc;
   std::vector<E> tile((size_t)d.T * d.pitch);
@@ -83,13 +130,22 @@ int validate_pass(const PassDesc& d) {
   const int np = (d.C / d.Cl) + (d.Tn / d.Tl) + (d.On / d.Ol) - 2;
   if (np != d.npeers || np < 1 || np > JD_MAX_PEERS) return JD_ERR_INVALID_ARG;
   if (d.T < 1 || d.pitch < 1 || d.logT < 0 || d.T != (1 << d.logT)) return JD_ERR_INVALID_ARG;
-  if (d.logW < 0 || (1 << d.logW) != (d.fft_mode == JD_COPY ? d.Cc : d.M)) return JD_ERR_INVALID_ARG;
+  if (d.fft_mode == JD_FFT_MIXED) {
+    // logW: log2 of the next power of two >= M
+    if (d.logW < 0 || (1 << d.logW) < d.M || (d.logW > 0 && (1 << (d.logW - 1)) >= d.M)) return JD_ERR_INVALID_ARG;
+  } else if (d.logW < 0 || (1 << d.logW) != (d.fft_mode == JD_COPY ? d.Cc : d.M)) {
+    return JD_ERR_INVALID_ARG;
+  }
   if (d.split_axis < 0 || d.split_axis > 3) return JD_ERR_INVALID_ARG;
   {
     const int want = d.Cl != d.C ? 1 : (d.Tl != d.Tn ? 2 : (d.Ol != d.On ? 3 : 0));
     if (want != d.split_axis) return JD_ERR_INVALID_ARG;
   }
-  if (d.intra_pad && (d.fft_mode == JD_COPY || d.M < 128 || d.use_bulk)) return JD_ERR_INVALID_ARG;
+  if (d.fft_mode == JD_FFT_MIXED) {
+    if (!d.intra_pad || d.use_bulk) return JD_ERR_INVALID_ARG;  // mixed-radix rows always use the padded layout
+  } else if (d.intra_pad && (d.fft_mode == JD_COPY || d.M < 128 || d.use_bulk)) {
+    return JD_ERR_INVALID_ARG;
+  }
   if (d.elem_bytes != 4 && d.elem_bytes != 8 && d.elem_bytes != 16) return JD_ERR_INVALID_ARG;
   if (d.load_t_contig ? d.is_t != 1 : d.is_c != 1) return JD_ERR_INVALID_ARG;
   if (d.store_t_contig ? d.os_t != 1 : d.os_c != 1) return JD_ERR_INVALID_ARG;
@@ -97,7 +153,12 @@ int validate_pass(const PassDesc& d) {
     if (d.Cc < 1 || d.pitch < d.Cc) return JD_ERR_INVALID_ARG;
   } else {
     if (d.elem_bytes == 4) return JD_ERR_INVALID_ARG;
-    if (d.M < 8 || (d.M & (d.M - 1))) return JD_ERR_INVALID_ARG;
+    if (d.fft_mode == JD_FFT_MIXED) {
+      MixedPlan pl;
+      if (d.M != d.C || !make_mixed_plan(d.M, &pl)) return JD_ERR_INVALID_ARG;
+    } else if (d.M < 8 || (d.M & (d.M - 1))) {
+      return JD_ERR_INVALID_ARG;
+    }
     if (d.pitch < padded_row_length(d.M, d.intra_pad) || !d.twiddle) return JD_ERR_INVALID_ARG;
     if (d.fft_mode == JD_FFT_POW2 && d.M != d.C) return JD_ERR_INVALID_ARG;
     if (d.fft_mode == JD_FFT_BLUESTEIN && (d.M < 2 * d.C - 1 || !d.chirp || !d.bhat)) return JD_ERR_INVALID_ARG;

@@ -88,7 +88,7 @@ JD_HD int fft_stage_radix_log(int logM, int s) {
 // eight consecutive outputs per thread (first stage, written as 16-byte
 // vectors), stride-8 groups (second stage) and unit stride (reads, later stages).
 JD_HD int padidx(int n, int pad) { return pad ? n + ((n >> 4) << 1) : n; }
-JD_HD int padded_row_length(int M, int pad) { return pad ? M + (M >> 3) : M; }
+JD_HD int padded_row_length(int M, int pad) { return pad ? M + (((M + 15) >> 4) << 1) : M; }
 
 template <typename R>
 JD_HD void stage_read(const cx<R>* row, int M, int j, cx<R> a[8], int pad) {

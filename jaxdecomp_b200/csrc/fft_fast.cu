@@ -38,6 +38,7 @@
 
 #include <cstdlib>
 
+#include "fft_radix.h"
 #include "launch.h"
 #include "tile_ops.h"
 
@@ -128,56 +129,6 @@ __device__ __forceinline__ void apply_tw(const cx<R>* __restrict__ tw, int idx, 
     a[FIRST + STRIDE * 14] = cmul(a[FIRST + STRIDE * 14], cmul(w6, w8));
     a[FIRST + STRIDE * 15] = cmul(a[FIRST + STRIDE * 15], cmul(w7, w8));
   }
-}
-
-// a * exp(-2 pi i K / 16), trivial cases resolved at compile time
-template <typename R, int K>
-__device__ __forceinline__ cx<R> mulw16(cx<R> a) {
-  constexpr int k = K & 15;
-  constexpr R c1 = (R)0.92387953251128673848, s1 = (R)0.38268343236508978178, h = (R)0.70710678118654752440;
-  if constexpr (k == 0) {
-    return a;
-  } else if constexpr (k == 4) {
-    return cx<R>{a.y, -a.x};
-  } else if constexpr (k == 8) {
-    return cx<R>{-a.x, -a.y};
-  } else if constexpr (k == 12) {
-    return cx<R>{-a.y, a.x};
-  } else if constexpr (k == 2) {
-    return cx<R>{(a.x + a.y) * h, (a.y - a.x) * h};
-  } else if constexpr (k == 6) {
-    return cx<R>{(a.y - a.x) * h, -(a.x + a.y) * h};
-  } else if constexpr (k == 10) {
-    return cx<R>{-(a.x + a.y) * h, (a.x - a.y) * h};
-  } else if constexpr (k == 14) {
-    return cx<R>{(a.x - a.y) * h, (a.x + a.y) * h};
-  } else {
-    // W = wr + i wi with wr = cos(pi k / 8), wi = -sin(pi k / 8)
-    constexpr R wr = (k == 1 || k == 15) ? c1 : (k == 3 || k == 13) ? s1 : (k == 5 || k == 11) ? -s1 : -c1;
-    constexpr R wi = (k == 1 || k == 7) ? -s1 : (k == 3 || k == 5) ? -c1 : (k == 9 || k == 15) ? s1 : c1;
-    return cx<R>{a.x * wr - a.y * wi, a.x * wi + a.y * wr};
-  }
-}
-
-// 16-point DFT in registers, natural order in and out (4 x 4 decomposition):
-// X[k1 + 4 k2] = sum_n W16^(n k1) W4^(n k2) sum_m x[n + 4 m] W4^(m k1)
-template <typename R>
-__device__ __forceinline__ void dft16(cx<R> (&a)[16]) {
-#pragma unroll
-  for (int n = 0; n < 4; ++n) dft4(a[n], a[n + 4], a[n + 8], a[n + 12]);  // a[n + 4 k1] = y_n[k1]
-  a[1 + 4] = mulw16<R, 1>(a[1 + 4]); a[1 + 8] = mulw16<R, 2>(a[1 + 8]); a[1 + 12] = mulw16<R, 3>(a[1 + 12]);
-  a[2 + 4] = mulw16<R, 2>(a[2 + 4]); a[2 + 8] = mulw16<R, 4>(a[2 + 8]); a[2 + 12] = mulw16<R, 6>(a[2 + 12]);
-  a[3 + 4] = mulw16<R, 3>(a[3 + 4]); a[3 + 8] = mulw16<R, 6>(a[3 + 8]); a[3 + 12] = mulw16<R, 9>(a[3 + 12]);
-  // second layer over n for each k1: inputs a[n + 4 k1], outputs X[k1 + 4 k2]
-  cx<R> t[16];
-#pragma unroll
-  for (int k1 = 0; k1 < 4; ++k1) {
-    cx<R> x0 = a[4 * k1], x1 = a[4 * k1 + 1], x2 = a[4 * k1 + 2], x3 = a[4 * k1 + 3];
-    dft4(x0, x1, x2, x3);
-    t[k1] = x0; t[k1 + 4] = x1; t[k1 + 8] = x2; t[k1 + 12] = x3;
-  }
-#pragma unroll
-  for (int k = 0; k < 16; ++k) a[k] = t[k];
 }
 
 // One stage on the sixteen values a[k] = row[j + k*M/16] of a thread.

@@ -1,0 +1,145 @@
+// Mixed-radix Stockham transform for lengths N = 2^a 3^b 5^c 7^d 11^e 13^f that
+// are not handled by the power-of-two kernels: the stage plan (built on the
+// host), the per-butterfly arithmetic shared by the CUDA kernel and the CPU
+// emulation, and the emulation's row driver.
+//
+// A stage of radix r works on N/r butterflies per row.  Butterfly bf reads
+// x[bf + q*N/r] (q < r), multiplies by the twiddles w_N^(q * kk * N/(Ls*r)),
+// applies an r-point DFT and writes y[(bf/Ls)*Ls*r + kk + q*Ls], where Ls is
+// the product of the earlier radices and kk = bf mod Ls.  Source and
+// destination are different buffers (ping-pong), so one barrier per stage is
+// enough.  Power-of-two radices come first: their Ls is a power of two
+// (shift and mask); for later stages bf/Ls is a multiply-high by a reciprocal.
+//
+// The reference covers such lengths through cuFFT plans (src/csrc/fft.cu:72-121).
+#pragma once
+#include "fft_radix.h"
+
+#define JD_MIXED_MAX_STAGES 12
+
+namespace jdb {
+
+struct MixedStage {
+  int32_t radix;
+  int32_t nb;        // butterflies per row: N / radix
+  int32_t ls;        // product of the earlier radices
+  int32_t ls_log;    // log2(ls) when ls is a power of two, else -1
+  int32_t tw_mul;    // N / (ls * radix): twiddle index of butterfly bf is (bf mod ls) * tw_mul
+  uint32_t ls_magic; // floor(2^32 / ls) + 1: bf / ls == mulhi(bf, ls_magic) for bf, ls < 2^16
+};
+
+struct MixedPlan {
+  int32_t n;
+  int32_t ns;
+  int32_t nb_min;    // butterflies per row of the stage with the largest radix
+  int32_t reserved;
+  MixedStage st[JD_MIXED_MAX_STAGES];
+};
+
+// Returns false when n has a prime factor above 13, is below 2, or needs too many stages.
+inline bool make_mixed_plan(int n, MixedPlan* out) {
+  if (n < 2 || n > 65535) return false;
+  int radices[32];
+  int ns = 0;
+  int m = n, a = 0;
+  while (m % 2 == 0) {
+    m /= 2;
+    ++a;
+  }
+  // power-of-two part: ceil(a/4) stages of nearly equal size, largest first
+  if (a > 0) {
+    const int k = (a + 3) / 4;
+    for (int i = 0; i < k; ++i) {
+      const int bits = a / k + (i < a % k ? 1 : 0);
+      radices[ns++] = 1 << bits;
+    }
+  }
+  const int primes[5] = {3, 5, 7, 11, 13};
+  for (int p : primes)
+    while (m % p == 0) {
+      if (ns >= 32) return false;
+      m /= p;
+      radices[ns++] = p;
+    }
+  if (m != 1 || ns > JD_MIXED_MAX_STAGES) return false;
+  MixedPlan pl{};
+  pl.n = n;
+  pl.ns = ns;
+  int ls = 1, rmax = 1;
+  for (int s = 0; s < ns; ++s) {
+    MixedStage& st = pl.st[s];
+    st.radix = radices[s];
+    st.nb = n / radices[s];
+    st.ls = ls;
+    st.ls_log = -1;
+    for (int l = 0; l < 31; ++l)
+      if ((1 << l) == ls) st.ls_log = l;
+    st.tw_mul = n / (ls * radices[s]);
+    st.ls_magic = (uint32_t)((0x100000000ULL / (uint64_t)ls) + 1ULL);
+    if (ls == 1) st.ls_magic = 0;  // unused: bf / 1 == bf
+    ls *= radices[s];
+    if (radices[s] > rmax) rmax = radices[s];
+  }
+  pl.nb_min = n / rmax;
+  *out = pl;
+  return true;
+}
+
+JD_HD uint32_t jd_mulhi(uint32_t a, uint32_t b) {
+#if defined(__CUDA_ARCH__)
+  return __umulhi(a, b);
+#else
+  return (uint32_t)(((uint64_t)a * (uint64_t)b) >> 32);
+#endif
+}
+
+// Twiddle + DFT of one butterfly held in a[]; returns the index of output 0
+// (output q goes to that index + q * st.ls).
+template <typename R, int RADIX>
+JD_HD int mixed_butterfly(const MixedStage& st, const cx<R>* tw, int bf, cx<R> (&a)[RADIX]) {
+  int kk = 0, blk = bf;
+  if (st.ls > 1) {
+    if (st.ls_log >= 0) {
+      kk = bf & (st.ls - 1);
+      blk = bf >> st.ls_log;
+    } else {
+      blk = (int)jd_mulhi((uint32_t)bf, st.ls_magic);
+      kk = bf - blk * st.ls;
+    }
+    twiddle_powers<R, RADIX>(tw, kk * st.tw_mul, a);
+  }
+  dft_any<R, RADIX>(a);
+  return blk * st.ls * RADIX + kk;
+}
+
+// One stage on one row, smem/host buffer to buffer (both in the padded layout of padidx).
+template <typename R, int RADIX>
+JD_HD void mixed_stage_row(const MixedStage& st, const cx<R>* tw, const cx<R>* src, cx<R>* dst, int first, int step) {
+  for (int bf = first; bf < st.nb; bf += step) {
+    cx<R> a[RADIX];
+#pragma unroll
+    for (int q = 0; q < RADIX; ++q) a[q] = src[padidx(bf + q * st.nb, 1)];
+    const int base = mixed_butterfly<R, RADIX>(st, tw, bf, a);
+#pragma unroll
+    for (int q = 0; q < RADIX; ++q) dst[padidx(base + q * st.ls, 1)] = a[q];
+  }
+}
+
+// Calls f.template run<RADIX>() for the stage's radix.
+template <typename F>
+JD_HD void mixed_dispatch(int radix, F&& f) {
+  switch (radix) {
+    case 2: f.template run<2>(); break;
+    case 3: f.template run<3>(); break;
+    case 4: f.template run<4>(); break;
+    case 5: f.template run<5>(); break;
+    case 7: f.template run<7>(); break;
+    case 8: f.template run<8>(); break;
+    case 11: f.template run<11>(); break;
+    case 13: f.template run<13>(); break;
+    case 16: f.template run<16>(); break;
+    default: break;
+  }
+}
+
+}  // namespace jdb

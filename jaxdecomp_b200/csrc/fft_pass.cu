@@ -263,6 +263,7 @@ int launch_pass(const PassDesc& d, void* stream_, StatusBlock* status) {
     const char* off = std::getenv("JD_B200_FAST");
     if (!(off && off[0] == '0')) return launch_fast_pass(d, stream_);
   }
+  if (d.fft_mode == JD_FFT_MIXED) return launch_mixed_pass(d, stream_);
   if (d.fft_mode == JD_COPY) {
     if (d.elem_bytes == 4) return launch_t<float, false, 1>(d, stream, status);
     if (d.elem_bytes == 8) return launch_t<cx<float>, false, 1>(d, stream, status);

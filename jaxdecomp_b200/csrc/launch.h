@@ -20,6 +20,8 @@ size_t pass_smem_bytes(const PassDesc& d);
 // Specialised kernel for power-of-two lengths 128..4096 (fft_fast.cu)
 bool fast_pass_eligible(const PassDesc& d);
 int launch_fast_pass(const PassDesc& d, void* stream);
+// Mixed-radix kernel for lengths with prime factors up to 13 (fft_mixed.cu)
+int launch_mixed_pass(const PassDesc& d, void* stream);
 
 // ---- cross-rank signalling (signal.cu) ---------------------------------------------------------------
 struct PeerFlags {

@@ -87,7 +87,9 @@ static std::map<std::tuple<int, int, int, bool>, TableSet> g_tables;  // (C, M, 
 
 FftTables get_fft_tables(int C, int M, int elem_bytes, bool device) {
   if (elem_bytes != 8 && elem_bytes != 16) throw std::runtime_error("tables: complex64/complex128 only");
-  if (M < 8 || (M & (M - 1))) throw std::runtime_error("tables: M must be a power of two >= 8");
+  // a table of M roots alone (mixed-radix transforms) may have any length; Bluestein needs a power of two
+  if (C != M && (M < 8 || (M & (M - 1)))) throw std::runtime_error("tables: M must be a power of two >= 8");
+  if (M < 1) throw std::runtime_error("tables: empty table");
   std::lock_guard<std::mutex> lk(g_mu);
   auto key = std::make_tuple(C, M, elem_bytes, device);
   auto it = g_tables.find(key);

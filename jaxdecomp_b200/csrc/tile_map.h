@@ -36,7 +36,9 @@
 
 namespace jdb {
 
-enum FftMode : int32_t { JD_COPY = 0, JD_FFT_POW2 = 1, JD_FFT_BLUESTEIN = 2 };
+// JD_FFT_MIXED: M == C is a product of the primes 2..13, transformed by the mixed-radix kernel; logW is
+// then the log2 of the next power of two >= M (only used to split loop counters into row and column).
+enum FftMode : int32_t { JD_COPY = 0, JD_FFT_POW2 = 1, JD_FFT_BLUESTEIN = 2, JD_FFT_MIXED = 3 };
 
 struct PassDesc {
   // strides in elements

@@ -59,12 +59,15 @@ JD_HD void tile_load(const PassDesc& d, E* tile, int o, int t0, int c0, int b, i
   const int cols = tile_cols(d, c0);
   const int pad = d.intra_pad;
   const E zero = zero_elem<E>();
+  // mixed-radix rows hold exactly C columns: nothing is stored past them
+  const int wlim = d.fft_mode == JD_FFT_MIXED ? cols : W;
   if (d.load_t_contig) {
     // lanes run along t (contiguous in memory), then along c
     if (d.vec_in && sizeof(E) == 8) {
       const int lh = logT - 1, Th = T >> 1;
       for (int e = tid; e < (W << lh); e += nt) {
         const int c = e >> lh, t = (e & (Th - 1)) << 1;
+        if (c >= wlim) continue;
         E v0 = zero, v1 = zero;
         if (c < cols && t0 + t < d.Tn) {
           const pair_of<E> p = *(const pair_of<E>*)(in + (long long)(c0 + c) * d.is_c + (t0 + t));
@@ -78,6 +81,7 @@ JD_HD void tile_load(const PassDesc& d, E* tile, int o, int t0, int c0, int b, i
     } else {
       for (int e = tid; e < (W << logT); e += nt) {
         const int c = e >> logT, t = e & (T - 1);
+        if (c >= wlim) continue;
         E v = zero;
         if (c < cols && t0 + t < d.Tn)
           v = prepare_value(d, in[(long long)(c0 + c) * d.is_c + (long long)(t0 + t) * d.is_t], c);
@@ -90,6 +94,7 @@ JD_HD void tile_load(const PassDesc& d, E* tile, int o, int t0, int c0, int b, i
       const int lh = logW - 1, Wh = W >> 1;
       for (int e = tid; e < (T << lh); e += nt) {
         const int t = e >> lh, c = (e & (Wh - 1)) << 1;
+        if (c >= wlim) continue;
         pair_of<E> p;
         p.a = zero;
         p.b = zero;
@@ -103,6 +108,7 @@ JD_HD void tile_load(const PassDesc& d, E* tile, int o, int t0, int c0, int b, i
     } else {
       for (int e = tid; e < (T << logW); e += nt) {
         const int t = e >> logW, c = e & (W - 1);
+        if (c >= wlim) continue;
         E v = zero;
         if (c < cols && t0 + t < d.Tn)
           v = prepare_value(d, in[(long long)(t0 + t) * d.is_t + (long long)(c0 + c) * d.is_c], c);

@@ -178,6 +178,28 @@ def _log2(n: int) -> int:
     return int(n).bit_length() - 1
 
 
+def mixed_radix_ok(n: int, elem_bytes: int) -> bool:
+    """True when a transform of length ``n`` can use the mixed-radix kernel: prime factors up to 13 and
+    two padded rows within the shared memory of one block (``JD_B200_MIXED=0`` forces Bluestein)."""
+    if os.environ.get("JD_B200_MIXED", "1") == "0" or n < 2:
+        return False
+    m = n
+    stages = 0
+    twos = 0
+    while m % 2 == 0:
+        m //= 2
+        twos += 1
+    stages += (twos + 3) // 4
+    for p in (3, 5, 7, 11, 13):
+        while m % p == 0:
+            m //= p
+            stages += 1
+    if m != 1 or stages > 12:
+        return False
+    rowlen = n + 2 * ((n + 15) // 16) + 16
+    return 2 * rowlen * elem_bytes <= 220 * 1024
+
+
 def choose_tiling(spec: PassSpec, elem_bytes: int, remote: bool) -> dict:
     """Pick the tile extents, shared-memory pitch and access-width flags."""
     C, Tn, On = spec.ext
@@ -189,7 +211,27 @@ def choose_tiling(spec: PassSpec, elem_bytes: int, remote: bool) -> dict:
     out = {"load_t_contig": int(load_t), "store_t_contig": int(store_t)}
     out["split_axis"] = 1 if Cl != C else (2 if Tl != Tn else (3 if Ol != On else 0))
     intra_pad = 0
-    if spec.fft:
+    if spec.fft and not (_is_pow2(C) and C >= 8) and mixed_radix_ok(C, elem_bytes):
+        # mixed-radix kernel: two shared-memory buffers of T padded rows
+        rowlen = C + 2 * ((C + 15) // 16)
+        pitch = rowlen + (2 - rowlen) % 16 if elem_bytes == 8 else rowlen + (1 - rowlen) % 8
+        tile_bytes = lambda t: 2 * t * pitch * elem_bytes  # noqa: E731
+        T = 1
+        while T < 32 and tile_bytes(2 * T) <= 110 * 1024:
+            T *= 2
+        if store_t:
+            # stored runs of at least 64 bytes, at the price of one resident block per SM
+            while T * elem_bytes < 64 and tile_bytes(2 * T) <= 220 * 1024:
+                T *= 2
+        T = min(T, _next_pow2(Tn))
+        ov = _env_int("JD_B200_TILE_T")
+        if ov:
+            T = max(1, min(_next_pow2(ov), 32))
+            while T > 1 and tile_bytes(T) > 220 * 1024:
+                T //= 2
+        out.update(fft_mode=3, M=C, T=T, Cc=C, pitch=pitch, logW=_log2(_next_pow2(C)))
+        intra_pad = 1
+    elif spec.fft:
         pow2 = _is_pow2(C) and C >= 8
         M = C if pow2 else max(8, _next_pow2(2 * C - 1))
         out["fft_mode"] = 1 if pow2 else 2

@@ -108,10 +108,12 @@ def test_invalid_descriptor_is_rejected():
         nat.run_pass_host(d)
 
 
-@pytest.mark.parametrize("n", [64, 128, 256, 512, 1024, 2048, 4096, 100, 384])
+@pytest.mark.parametrize("n", [64, 128, 256, 512, 1024, 2048, 4096, 100, 384,
+                               2, 4, 6, 12, 30, 77, 143, 768, 1000, 1365, 1536, 2310, 34, 97])
 @pytest.mark.parametrize("dtype", [torch.complex64, torch.complex128])
 def test_row_transforms_all_stage_structures(n, dtype):
-    """Every radix structure (8.8.2, 8.8.4, 8.8.8, ...) with intra-row padding,
+    """Every radix structure (8.8.2, 8.8.4, 8.8.8, ...) with intra-row padding, mixed-radix lengths
+    covering the radices 2..16 and the primes up to 13, and Bluestein lengths (34, 97);
     contiguous and strided, forward and inverse."""
     x = torch.randn((3, 4, n), dtype=dtype, generator=torch.Generator().manual_seed(n))
     tol = 3e-6 if dtype == torch.complex64 else 1e-13
@@ -125,3 +127,22 @@ def test_row_transforms_all_stage_structures(n, dtype):
     out = emulate.emulate_steps([y], [plan.Fft(0)], (1, 1))[0]
     ref = torch.fft.fft(y, dim=0)
     assert (out - ref).abs().max() <= tol * ref.abs().max()
+
+
+def test_mixed_radix_selection():
+    """Lengths with prime factors up to 13 take the mixed-radix mode, others Bluestein, powers of two >= 8 their own."""
+    from jaxdecomp_b200.ops import passes
+
+    def mode(n):
+        specs, _ = passes.compile_passes([plan.Fft(2)], (2, 4, n), (1, 1), (0, 0))
+        return passes.choose_tiling(specs[0], 8, False)
+
+    assert mode(768)["fft_mode"] == 3 and mode(768)["M"] == 768
+    assert mode(1000)["fft_mode"] == 3
+    assert mode(4)["fft_mode"] == 3
+    assert mode(1024)["fft_mode"] == 1
+    assert mode(34)["fft_mode"] == 2 and mode(34)["M"] == 128
+    t = mode(768)
+    assert t["intra_pad"] == 1 and t["pitch"] % 16 == 2 and t["pitch"] >= 768 + 2 * 48
+    assert 2 * t["T"] * t["pitch"] * 8 <= 226 * 1024
+    assert not passes.mixed_radix_ok(2 * 17, 8)

@@ -18,7 +18,10 @@ def _rel(a, b):
 
 
 @pytest.mark.parametrize("shape", [(64, 32, 128), (8, 16, 8), (256, 8, 1024), (16, 16, 2048), (24, 40, 58), (29, 19, 17),
-                                   (4, 2, 4096), (128, 128, 128), (256, 64, 512), (32, 4096, 64), (2048, 32, 256)])
+                                   (4, 2, 4096), (128, 128, 128), (256, 64, 512), (32, 4096, 64), (2048, 32, 256),
+                                   # mixed-radix lengths: every radix, ragged tiles, one and two blocks per SM
+                                   (96, 60, 768), (100, 30, 1000), (12, 6, 2310), (77, 143, 26), (4, 2, 6),
+                                   (1536, 8, 384), (7, 11, 13), (33, 21, 45), (20, 1365, 3072)])
 @pytest.mark.parametrize("dtype", [torch.complex64, torch.complex128])
 def test_fft_single_gpu(shape, dtype):
     x = torch.randn(shape, device=_dev(), dtype=dtype)
@@ -55,6 +58,15 @@ def test_fft_non_contiguous_mode_and_batch():
     jd.config.update("transpose_axis_contiguous", True)
     k = jd.pfft3d(x, backend="b200")
     assert _rel(k, torch.fft.fftn(x, dim=(1, 2, 3)).permute(0, 2, 3, 1)) < 3e-6
+    # strided mixed-radix transforms
+    jd.config.update("transpose_axis_contiguous", False)
+    try:
+        y = torch.randn((2, 48, 36, 60), device=_dev(), dtype=torch.complex128)
+        k = jd.pfft3d(y, backend="b200")
+        assert _rel(k, torch.fft.fftn(y, dim=(1, 2, 3))) < 1e-13
+        assert _rel(jd.pifft3d(k, backend="b200"), y) < 1e-12
+    finally:
+        jd.config.update("transpose_axis_contiguous", True)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float64, torch.complex64, torch.complex128])
