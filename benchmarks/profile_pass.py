@@ -25,11 +25,13 @@ def main():
     ap.add_argument("--size", type=int, default=512)
     ap.add_argument("--dtype", default="c64", choices=["c64", "c128"])
     ap.add_argument("--reps", type=int, default=3)
+    ap.add_argument("--shape", type=int, nargs=3, default=None, help="block shape instead of size^3 "
+                    "(the passes transform the last axis)")
     args = ap.parse_args()
     n = args.size
     dt = torch.complex64 if args.dtype == "c64" else torch.complex128
     mesh = jd.single_rank_mesh()
-    x = torch.randn((n, n, n), device="cuda", dtype=dt)
+    x = torch.randn(tuple(args.shape) if args.shape else (n, n, n), device="cuda", dtype=dt)
     rot = [plan.Fft(2), plan.Perm(plan.ROT_FWD)]
     pln = [plan.Fft(2)]
     nbytes = 2 * x.numel() * x.element_size()

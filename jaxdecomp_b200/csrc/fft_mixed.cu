@@ -20,6 +20,8 @@
 // (src/csrc/fft.cu:72-121).
 #include <cuda_runtime.h>
 
+#include <cstdlib>
+
 #include "fft_mixed.h"
 #include "launch.h"
 #include "tile_ops.h"
@@ -142,13 +144,9 @@ __global__ void __launch_bounds__(sizeof(R) == 4 ? 512 : 256, 2)
 }
 
 // ---- host side --------------------------------------------------------------------------------------------------
-// Threads per row: the butterflies of the largest-radix stage, spread over more
-// rounds when T rows of them exceed the block size the register budget allows.
 static int mixed_threads(const PassDesc& d, const MixedPlan& pl, int* tpr_out) {
-  const int cap = d.elem_bytes == 8 ? 512 : 256;
-  int tpr = pl.nb_min;
-  for (int k = 2; (long long)d.T * tpr > cap && tpr > 1; ++k) tpr = (pl.nb_min + k - 1) / k;
-  if ((long long)d.T * tpr > cap) return 0;
+  const int tpr = mixed_threads_per_row(pl.nb_min, d.T, d.elem_bytes);
+  if (tpr <= 0) return 0;
   *tpr_out = tpr;
   int nt = d.T * tpr;
   nt = (nt + 31) / 32 * 32;
@@ -207,6 +205,14 @@ int launch_mixed_pass(const PassDesc& d, void* stream) {
   if (d.fft_mode != JD_FFT_MIXED || !make_mixed_plan(d.M, &pl)) {
     set_last_error("mixed-radix pass: length has a prime factor above 13");
     return JD_ERR_INVALID_ARG;
+  }
+  if (d.elem_bytes != 8 && d.elem_bytes != 16) return JD_ERR_INVALID_ARG;
+  const char* env = std::getenv("JD_B200_MIXED_STATIC");
+  if (!(env && env[0] == '0')) {
+    for (auto fn : {launch_mixed_static_a, launch_mixed_static_b, launch_mixed_static_c}) {
+      const int rc = fn(d, stream);
+      if (rc != JD_ERR_UNSUPPORTED) return rc;
+    }
   }
   if (d.elem_bytes == 8) return launch_mixed_r<float>(d, pl, (cudaStream_t)stream);
   if (d.elem_bytes == 16) return launch_mixed_r<double>(d, pl, (cudaStream_t)stream);

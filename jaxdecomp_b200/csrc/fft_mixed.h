@@ -36,10 +36,12 @@ struct MixedPlan {
   MixedStage st[JD_MIXED_MAX_STAGES];
 };
 
-// Returns false when n has a prime factor above 13, is below 2, or needs too many stages.
-inline bool make_mixed_plan(int n, MixedPlan* out) {
-  if (n < 2 || n > 65535) return false;
-  int radices[32];
+// The plan for length n; ns == 0 when n has a prime factor above 13, is below 2, or needs too many
+// stages.  constexpr so that kernels specialised on the length can fold every stage constant.
+constexpr MixedPlan mixed_plan_of(int n) {
+  MixedPlan pl{};
+  if (n < 2 || n > 65535) return pl;
+  int radices[32] = {};
   int ns = 0;
   int m = n, a = 0;
   while (m % 2 == 0) {
@@ -55,34 +57,48 @@ inline bool make_mixed_plan(int n, MixedPlan* out) {
     }
   }
   const int primes[5] = {3, 5, 7, 11, 13};
-  for (int p : primes)
+  for (int pi = 0; pi < 5; ++pi) {
+    const int p = primes[pi];
     while (m % p == 0) {
-      if (ns >= 32) return false;
+      if (ns >= 32) return pl;
       m /= p;
       radices[ns++] = p;
     }
-  if (m != 1 || ns > JD_MIXED_MAX_STAGES) return false;
-  MixedPlan pl{};
+  }
+  if (m != 1 || ns > JD_MIXED_MAX_STAGES) return pl;
   pl.n = n;
   pl.ns = ns;
   int ls = 1, rmax = 1;
   for (int s = 0; s < ns; ++s) {
-    MixedStage& st = pl.st[s];
-    st.radix = radices[s];
-    st.nb = n / radices[s];
-    st.ls = ls;
-    st.ls_log = -1;
+    pl.st[s].radix = radices[s];
+    pl.st[s].nb = n / radices[s];
+    pl.st[s].ls = ls;
+    pl.st[s].ls_log = -1;
     for (int l = 0; l < 31; ++l)
-      if ((1 << l) == ls) st.ls_log = l;
-    st.tw_mul = n / (ls * radices[s]);
-    st.ls_magic = (uint32_t)((0x100000000ULL / (uint64_t)ls) + 1ULL);
-    if (ls == 1) st.ls_magic = 0;  // unused: bf / 1 == bf
+      if ((1 << l) == ls) pl.st[s].ls_log = l;
+    pl.st[s].tw_mul = n / (ls * radices[s]);
+    pl.st[s].ls_magic = ls == 1 ? 0u : (uint32_t)((0x100000000ULL / (unsigned long long)ls) + 1ULL);
     ls *= radices[s];
     if (radices[s] > rmax) rmax = radices[s];
   }
   pl.nb_min = n / rmax;
+  return pl;
+}
+
+inline bool make_mixed_plan(int n, MixedPlan* out) {
+  const MixedPlan pl = mixed_plan_of(n);
+  if (pl.ns == 0) return false;
   *out = pl;
   return true;
+}
+
+// Threads per row for tiles of T rows: the butterflies of the largest-radix stage, spread over more
+// rounds when T rows of them exceed the block size that the register budget allows (0: impossible).
+constexpr int mixed_threads_per_row(int nb_min, int T, int elem_bytes) {
+  const int cap = elem_bytes == 8 ? 512 : 256;
+  int tpr = nb_min;
+  for (int k = 2; T * tpr > cap && tpr > 1; ++k) tpr = (nb_min + k - 1) / k;
+  return T * tpr > cap ? 0 : tpr;
 }
 
 JD_HD uint32_t jd_mulhi(uint32_t a, uint32_t b) {

@@ -1,0 +1,261 @@
+// Mixed-radix tile pass specialised on the transform length: same algorithm
+// and data path as fft_mixed.cu (first stage from global memory, ping-pong
+// stages in shared memory, direct or transposed store), but the stage plan,
+// the tile height, the row pitch and the thread layout are compile-time
+// constants, so the per-element index arithmetic (the limiter of the generic
+// kernel: 146 instructions per element, two thirds of them integer) folds
+// into immediates.  Instantiated for the common lengths 2^k * {3, 5, 7, 9, 15,
+// 25, 125} in fft_mixed_s*.cu; other lengths use the generic kernel.
+#pragma once
+#include <cuda_runtime.h>
+
+#include "fft_mixed.h"
+#include "launch.h"
+#include "tile_ops.h"
+
+namespace jdb {
+
+// Geometry rules; ops/passes.py::choose_tiling applies the same ones, and the launcher falls back to
+// the generic kernel when a descriptor was tiled differently.
+constexpr int mixed_static_pitch(int n, int elem_bytes) {
+  const int rowlen = n + 2 * ((n + 15) / 16);
+  return elem_bytes == 8 ? rowlen + (((2 - rowlen) % 16) + 16) % 16 : rowlen + (((1 - rowlen) % 8) + 8) % 8;
+}
+constexpr int mixed_static_T(int n, int elem_bytes, bool store_t) {
+  const int pitch = mixed_static_pitch(n, elem_bytes);
+  int T = 1;
+  while (T < 32 && 2 * (2 * T) * pitch * elem_bytes <= 110 * 1024) T *= 2;
+  if (store_t)
+    while (T * elem_bytes < 64 && 2 * (2 * T) * pitch * elem_bytes <= 220 * 1024) T *= 2;
+  return T;
+}
+
+template <typename R, int N_, int T_, bool DOUT_>
+struct MixedCfg {
+  static constexpr int N = N_, T = T_;
+  static constexpr bool DOUT = DOUT_;
+  static constexpr int EB = 2 * (int)sizeof(R);
+  static constexpr MixedPlan PL = mixed_plan_of(N);
+  static constexpr int NS = PL.ns;
+  static constexpr int PITCH = mixed_static_pitch(N, EB);
+  static constexpr int TPR = mixed_threads_per_row(PL.nb_min, T, EB);
+  static constexpr int NT = (T * TPR + 31) / 32 * 32;
+  static constexpr size_t SMEM = 2 * (size_t)T * PITCH * EB;
+  static constexpr int MINB = SMEM * 2 + 2048 <= 227 * 1024 ? 2 : 1;
+  static_assert(NS > 0 && TPR > 0, "length not supported by the mixed-radix plan");
+  static_assert(SMEM <= 226 * 1024, "tile exceeds shared memory");
+};
+
+// Stage S of the plan on the butterflies of one thread.  SG: inputs come from global memory; DG: outputs go
+// to global memory.
+template <typename Cfg, typename R, int S, bool SG, bool DG>
+__device__ __forceinline__ void static_stage(const PassDesc& d, const cx<R>* __restrict__ tw, const cx<R>* src, cx<R>* dst,
+                                             const cx<R>* __restrict__ gsrc, int j, bool inv, bool do_scale, R scale,
+                                             int peer0, long long toff) {
+  using E = cx<R>;
+  constexpr int RADIX = Cfg::PL.st[S].radix, NB = Cfg::PL.st[S].nb, LS = Cfg::PL.st[S].ls, TWM = Cfg::PL.st[S].tw_mul;
+  constexpr int TPR = Cfg::TPR;
+  constexpr int ITERS = (NB + TPR - 1) / TPR;
+#pragma unroll
+  for (int it = 0; it < ITERS; ++it) {
+    const int bf = j + it * TPR;
+    if ((NB % TPR) != 0 && it == ITERS - 1 && bf >= NB) break;
+    E a[RADIX];
+    if constexpr (SG) {
+#pragma unroll
+      for (int q = 0; q < RADIX; ++q) a[q] = gsrc[bf + q * NB];
+      if (inv) {
+#pragma unroll
+        for (int q = 0; q < RADIX; ++q) a[q] = cswap(a[q]);
+      }
+    } else if constexpr (NB % 16 == 0) {
+      const E* p = src + padidx(bf, 1);  // the padded distance is linear when NB is a multiple of 16
+#pragma unroll
+      for (int q = 0; q < RADIX; ++q) a[q] = p[q * (NB + NB / 8)];
+    } else {
+#pragma unroll
+      for (int q = 0; q < RADIX; ++q) a[q] = src[padidx(bf + q * NB, 1)];
+    }
+    int kk = 0, blk = bf;
+    if constexpr (LS > 1) {
+      blk = bf / LS;
+      kk = bf - blk * LS;
+      twiddle_powers<R, RADIX>(tw, kk * TWM, a);
+    }
+    dft_any<R, RADIX>(a);
+    const int base = blk * (LS * RADIX) + kk;
+    if constexpr (DG) {
+#pragma unroll
+      for (int q = 0; q < RADIX; ++q) {
+        const int c = base + q * LS;
+        E v = a[q];
+        if (inv) v = cswap(v);
+        if (do_scale) v = cscale(v, scale);
+        const int pc = d.split_axis == 1 ? c / d.Cl : 0;
+        ((E*)d.out[peer0 + pc])[toff + (c - pc * d.Cl)] = v;
+      }
+    } else if constexpr (LS % 16 == 0) {
+      E* p = dst + padidx(base, 1);
+#pragma unroll
+      for (int q = 0; q < RADIX; ++q) p[q * (LS + LS / 8)] = a[q];
+    } else if constexpr (LS == 1 && (RADIX == 16 || RADIX == 8 || RADIX == 4 || RADIX == 2)) {
+      // RADIX consecutive columns starting at a multiple of RADIX: inside one padded group of sixteen
+      cx2<R>* v = reinterpret_cast<cx2<R>*>(dst + padidx(base, 1));
+#pragma unroll
+      for (int q = 0; q < RADIX / 2; ++q) v[q] = cx2<R>{a[2 * q], a[2 * q + 1]};
+    } else {
+#pragma unroll
+      for (int q = 0; q < RADIX; ++q) dst[padidx(base + q * LS, 1)] = a[q];
+    }
+  }
+}
+
+template <typename Cfg, typename R, int S>
+__device__ __forceinline__ void static_stages(const PassDesc& d, const cx<R>* tw, cx<R>* buf0, cx<R>* buf1,
+                                              const cx<R>* gsrc, int row, int j, bool active, bool inv, bool do_scale,
+                                              R scale, int peer0, long long toff) {
+  using E = cx<R>;
+  constexpr bool SG = S == 0;
+  constexpr bool DG = Cfg::DOUT && S == Cfg::NS - 1;
+  // stage 0 writes buffer 0, stage 1 reads it and writes buffer 1, ...
+  const E* src = ((S - 1) % 2 == 0 ? buf0 : buf1) + row * Cfg::PITCH;
+  E* dst = (S % 2 == 0 ? buf0 : buf1) + row * Cfg::PITCH;
+  if (active) static_stage<Cfg, R, S, SG, DG>(d, tw, src, dst, gsrc, j, inv, do_scale, scale, peer0, toff);
+  if constexpr (!DG) __syncthreads();
+  if constexpr (S + 1 < Cfg::NS)
+    static_stages<Cfg, R, S + 1>(d, tw, buf0, buf1, gsrc, row, j, active, inv, do_scale, scale, peer0, toff);
+}
+
+// Transposed store of the finished tile: every thread writes 16 contiguous bytes along the destination's
+// fastest axis (two rows of one column for complex64, one element for complex128).
+template <typename Cfg, typename R>
+__device__ __forceinline__ void static_rot_store(const PassDesc& d, const cx<R>* res, int o, int t0, int b, bool inv,
+                                                 bool do_scale, R scale) {
+  using E = cx<R>;
+  constexpr int PER16 = 16 / Cfg::EB;
+  constexpr int TP = Cfg::T / PER16 < 1 ? 1 : Cfg::T / PER16;  // threads that share one column
+  constexpr int CSTEP = Cfg::NT / TP;                          // columns advanced per iteration
+  const int tid = threadIdx.x;
+  const int tp = tid % TP;
+  const int cs = tid / TP;
+  const int t = tp * (Cfg::T >= PER16 ? PER16 : 1);
+  const int tg = t0 + t;
+  if (tg >= d.Tn) return;
+  const OutBase ob = out_base_for(d, o, b);
+  const int pt = d.split_axis == 2 ? tg / d.Tl : 0;
+  const long long toff = ob.off + (long long)(tg - pt * d.Tl) * d.os_t;
+  const E* src = res + t * Cfg::PITCH;
+  int pc = 0, cl = cs;
+  if (d.split_axis == 1) {
+    pc = cs / d.Cl;
+    cl = cs - pc * d.Cl;
+  }
+#pragma unroll 4
+  for (int c = cs; c < Cfg::N; c += CSTEP) {
+    E* dst = (E*)d.out[ob.peer + pc + pt] + (toff + (long long)cl * d.os_c);
+    const int col = padidx(c, 1);
+    E v0 = src[col];
+    if (inv) v0 = cswap(v0);
+    if (do_scale) v0 = cscale(v0, scale);
+    if constexpr (PER16 == 2 && Cfg::T >= 2) {
+      E v1 = src[Cfg::PITCH + col];
+      if (inv) v1 = cswap(v1);
+      if (do_scale) v1 = cscale(v1, scale);
+      *reinterpret_cast<cx2<R>*>(dst) = cx2<R>{v0, v1};
+    } else {
+      *dst = v0;
+    }
+    cl += CSTEP;
+    if (d.split_axis == 1)
+      while (cl >= d.Cl) {
+        cl -= d.Cl;
+        ++pc;
+      }
+  }
+}
+
+template <typename R, int N, int T, bool DOUT>
+__global__ void __launch_bounds__((MixedCfg<R, N, T, DOUT>::NT), (MixedCfg<R, N, T, DOUT>::MINB))
+    fft_mixed_static_kernel(const __grid_constant__ PassDesc d) {
+  using Cfg = MixedCfg<R, N, T, DOUT>;
+  using E = cx<R>;
+  extern __shared__ __align__(16) unsigned char mixed_static_smem[];
+  E* buf0 = reinterpret_cast<E*>(mixed_static_smem);
+  E* buf1 = buf0 + (size_t)T * Cfg::PITCH;
+
+  const int tid = threadIdx.x;
+  const int tiles_t = (d.Tn + T - 1) / T;
+  const int tt = blockIdx.x % tiles_t;
+  const int o = blockIdx.x / tiles_t;
+  const int b = blockIdx.y;
+  const int t0 = tt * T;
+  const int row = tid / Cfg::TPR;
+  const int j = tid - row * Cfg::TPR;
+  const bool active = row < T && t0 + row < d.Tn;
+  const bool inv = d.inverse != 0;
+  const E* gsrc = (const E*)d.in + ((long long)o * d.is_o + (long long)b * d.is_b + (long long)(t0 + row) * d.is_t);
+  const OutBase ob = out_base_for(d, o, b);
+  const int t = t0 + row;
+  const int pt = d.split_axis == 2 ? t / d.Tl : 0;
+  const long long toff = ob.off + (long long)(t - pt * d.Tl) * d.os_t;
+  const R scale = (R)d.scale;
+  const bool do_scale = d.scale != 1.0;
+  static_stages<Cfg, R, 0>(d, (const E*)d.twiddle, buf0, buf1, gsrc, row, j, active, inv, do_scale, scale, ob.peer + pt,
+                           toff);
+  if constexpr (!DOUT) {
+    // the last stage (index NS-1) wrote buffer (NS-1) % 2
+    static_rot_store<Cfg, R>(d, (Cfg::NS - 1) % 2 == 0 ? buf0 : buf1, o, t0, b, inv, do_scale, scale);
+  }
+}
+
+template <typename R, int N, int T, bool DOUT>
+static int launch_mixed_static_t(const PassDesc& d, cudaStream_t stream) {
+  using Cfg = MixedCfg<R, N, T, DOUT>;
+  auto kern = fft_mixed_static_kernel<R, N, T, DOUT>;
+  static bool configured = false;  // one flag per template instantiation
+  if (Cfg::SMEM > 48 * 1024 && !configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM);
+    if (e != cudaSuccess) {
+      set_last_error(cudaGetErrorString(e));
+      return JD_ERR_CUDA;
+    }
+    configured = true;
+  }
+  const long long nblocks = (long long)((d.Tn + T - 1) / T) * d.On;
+  if (nblocks > 2147483647LL || d.B > 65535) {
+    set_last_error("mixed-radix pass: grid too large");
+    return JD_ERR_INVALID_ARG;
+  }
+  kern<<<dim3((unsigned)nblocks, (unsigned)d.B, 1), Cfg::NT, Cfg::SMEM, stream>>>(d);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_last_error(cudaGetErrorString(e));
+    return JD_ERR_CUDA;
+  }
+  return JD_OK;
+}
+
+// JD_ERR_UNSUPPORTED: the descriptor does not match the specialised geometry (strided load, other tile height
+// or pitch, unaligned transposed store): the caller uses the generic kernel.
+template <typename R, int N>
+static int launch_mixed_static_n(const PassDesc& d, cudaStream_t stream) {
+  constexpr int EB = 2 * (int)sizeof(R);
+  if (d.load_t_contig || d.is_c != 1 || d.M != N || d.pitch != mixed_static_pitch(N, EB)) return JD_ERR_UNSUPPORTED;
+  if (!d.store_t_contig) {
+    constexpr int T = mixed_static_T(N, EB, false);
+    if (d.os_c != 1 || d.T != T) return JD_ERR_UNSUPPORTED;
+    return launch_mixed_static_t<R, N, T, true>(d, stream);
+  }
+  constexpr int T = mixed_static_T(N, EB, true);
+  if (d.os_t != 1 || d.T != T) return JD_ERR_UNSUPPORTED;
+  if (EB == 8 && T >= 2) {
+    // 16-byte stores of two rows: every address component must be even
+    if ((d.Tl & 1) || (d.Tn & 1) || (d.out_base & 1) || (d.os_c & 1) || (d.os_o & 1) || (d.os_b & 1))
+      return JD_ERR_UNSUPPORTED;
+    for (int p = 0; p < d.npeers; ++p)
+      if ((uintptr_t)d.out[p] % 16) return JD_ERR_UNSUPPORTED;
+  }
+  return launch_mixed_static_t<R, N, T, false>(d, stream);
+}
+
+}  // namespace jdb

@@ -22,6 +22,10 @@ bool fast_pass_eligible(const PassDesc& d);
 int launch_fast_pass(const PassDesc& d, void* stream);
 // Mixed-radix kernel for lengths with prime factors up to 13 (fft_mixed.cu)
 int launch_mixed_pass(const PassDesc& d, void* stream);
+// Length-specialised variants (fft_mixed_s*.cu); JD_ERR_UNSUPPORTED when the length or the tiling is not theirs
+int launch_mixed_static_a(const PassDesc& d, void* stream);
+int launch_mixed_static_b(const PassDesc& d, void* stream);
+int launch_mixed_static_c(const PassDesc& d, void* stream);
 
 // ---- cross-rank signalling (signal.cu) ---------------------------------------------------------------
 struct PeerFlags {

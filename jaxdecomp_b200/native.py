@@ -39,7 +39,7 @@ SOURCES = [
     "trace.cpp",
     "cpu_ref.cpp",
     "fft_pass.cu",
-    "fft_fast.cu", "fft_mixed.cu",
+    "fft_fast.cu", "fft_mixed.cu", "fft_mixed_sa.cu", "fft_mixed_sb.cu", "fft_mixed_sc.cu",
     "signal.cu",
     "halo.cu",
     "cic.cu",

@@ -39,6 +39,27 @@ def test_fft_single_gpu(shape, dtype):
                                    atol=1e-4 if dtype == torch.complex64 else 1e-10)
 
 
+_STATIC_LENGTHS = [96, 192, 384, 768, 1536, 3072, 288, 576, 1152, 2304, 160, 320, 640, 1280, 2560, 200, 400, 800, 1600,
+                   250, 500, 1000, 2000, 240, 480, 960, 1920, 448, 896, 1792]
+
+
+@pytest.mark.parametrize("dtype", [torch.complex64, torch.complex128])
+def test_mixed_radix_specialised_lengths(dtype, monkeypatch):
+    """Every length with a specialised mixed-radix kernel, as the rotating first pass and as the plain last pass,
+    against torch.fft and against the generic mixed-radix kernel."""
+    tol = 3e-6 if dtype == torch.complex64 else 1e-13
+    for n in _STATIC_LENGTHS:
+        for shape in ((16, 32, n), (n, 16, 32)):
+            x = torch.randn(shape, device=_dev(), dtype=dtype)
+            k = jd.pfft3d(x, backend="b200")
+            ref = torch.fft.fftn(x).permute(1, 2, 0)
+            assert _rel(k, ref) < tol, (n, shape)
+            assert _rel(jd.pifft3d(k, backend="b200"), x) < 10 * tol, (n, shape)
+    monkeypatch.setenv("JD_B200_MIXED_STATIC", "0")
+    x = torch.randn((16, 32, 768), device=_dev(), dtype=dtype)
+    assert _rel(jd.pfft3d(x, backend="b200"), torch.fft.fftn(x).permute(1, 2, 0)) < tol
+
+
 @pytest.mark.parametrize("bulk,tile", [("0", ""), ("1", "4"), ("1", "16"), ("0", "2")])
 def test_fft_load_paths_and_tiles(bulk, tile, monkeypatch):
     monkeypatch.setenv("JD_B200_BULK", bulk)
