@@ -145,7 +145,7 @@ __global__ void __launch_bounds__(sizeof(R) == 4 ? 512 : 256, 2)
 
 // ---- host side --------------------------------------------------------------------------------------------------
 static int mixed_threads(const PassDesc& d, const MixedPlan& pl, int* tpr_out) {
-  const int tpr = mixed_threads_per_row(pl.nb_min, d.T, d.elem_bytes);
+  const int tpr = mixed_threads_per_row(pl, d.T, d.elem_bytes);
   if (tpr <= 0) return 0;
   *tpr_out = tpr;
   int nt = d.T * tpr;

@@ -8,8 +8,8 @@
 // applies an r-point DFT and writes y[(bf/Ls)*Ls*r + kk + q*Ls], where Ls is
 // the product of the earlier radices and kk = bf mod Ls.  Source and
 // destination are different buffers (ping-pong), so one barrier per stage is
-// enough.  Power-of-two radices come first: their Ls is a power of two
-// (shift and mask); for later stages bf/Ls is a multiply-high by a reciprocal.
+// enough.  Radices are the primes up to 13 and 4, 6, 8, 10, 12, 15, 16; where Ls
+// is a power of two bf/Ls is a shift, elsewhere a multiply-high by a reciprocal.
 //
 // The reference covers such lengths through cuFFT plans (src/csrc/fft.cu:72-121).
 #pragma once
@@ -36,6 +36,22 @@ struct MixedPlan {
   MixedStage st[JD_MIXED_MAX_STAGES];
 };
 
+// Stage radices for lengths that profit from composite butterflies (fewer stages, or stages whose
+// butterfly counts divide evenly among the threads of a row).  Found by an exhaustive search over the
+// factorisations into radices <= 16, scored by padded work per stage plus a fixed cost per stage.
+struct MixedRadices {
+  int32_t n;
+  int32_t r[4];
+};
+constexpr MixedRadices kMixedRadixTable[] = {
+    {96, {12, 8, 0, 0}},    {192, {8, 8, 3, 0}},    {384, {8, 8, 6, 0}},     {1536, {16, 16, 6, 0}},
+    {3072, {16, 16, 12, 0}}, {288, {12, 6, 4, 0}},   {576, {12, 12, 4, 0}},   {1152, {12, 12, 8, 0}},
+    {2304, {16, 12, 12, 0}}, {160, {16, 10, 0, 0}},  {2560, {16, 16, 10, 0}}, {400, {10, 10, 4, 0}},
+    {800, {10, 10, 8, 0}},   {1600, {16, 10, 10, 0}}, {250, {10, 5, 5, 0}},    {500, {10, 10, 5, 0}},
+    {1000, {10, 10, 10, 0}}, {2000, {10, 10, 5, 4}}, {240, {16, 15, 0, 0}},   {480, {12, 10, 4, 0}},
+    {960, {15, 8, 8, 0}},    {1920, {16, 15, 8, 0}},
+};
+
 // The plan for length n; ns == 0 when n has a prime factor above 13, is below 2, or needs too many
 // stages.  constexpr so that kernels specialised on the length can fold every stage constant.
 constexpr MixedPlan mixed_plan_of(int n) {
@@ -43,29 +59,34 @@ constexpr MixedPlan mixed_plan_of(int n) {
   if (n < 2 || n > 65535) return pl;
   int radices[32] = {};
   int ns = 0;
-  int m = n, a = 0;
-  while (m % 2 == 0) {
-    m /= 2;
-    ++a;
-  }
-  // power-of-two part: ceil(a/4) stages of nearly equal size, largest first
-  if (a > 0) {
-    const int k = (a + 3) / 4;
-    for (int i = 0; i < k; ++i) {
-      const int bits = a / k + (i < a % k ? 1 : 0);
-      radices[ns++] = 1 << bits;
+  for (const MixedRadices& e : kMixedRadixTable)
+    if (e.n == n)
+      for (int i = 0; i < 4 && e.r[i] > 0; ++i) radices[ns++] = e.r[i];
+  if (ns == 0) {
+    int m = n, a = 0;
+    while (m % 2 == 0) {
+      m /= 2;
+      ++a;
     }
-  }
-  const int primes[5] = {3, 5, 7, 11, 13};
-  for (int pi = 0; pi < 5; ++pi) {
-    const int p = primes[pi];
-    while (m % p == 0) {
-      if (ns >= 32) return pl;
-      m /= p;
-      radices[ns++] = p;
+    // power-of-two part: ceil(a/4) stages of nearly equal size, largest first
+    if (a > 0) {
+      const int k = (a + 3) / 4;
+      for (int i = 0; i < k; ++i) {
+        const int bits = a / k + (i < a % k ? 1 : 0);
+        radices[ns++] = 1 << bits;
+      }
     }
+    const int primes[5] = {3, 5, 7, 11, 13};
+    for (int pi = 0; pi < 5; ++pi) {
+      const int p = primes[pi];
+      while (m % p == 0) {
+        if (ns >= 32) return pl;
+        m /= p;
+        radices[ns++] = p;
+      }
+    }
+    if (m != 1 || ns > JD_MIXED_MAX_STAGES) return pl;
   }
-  if (m != 1 || ns > JD_MIXED_MAX_STAGES) return pl;
   pl.n = n;
   pl.ns = ns;
   int ls = 1, rmax = 1;
@@ -92,13 +113,34 @@ inline bool make_mixed_plan(int n, MixedPlan* out) {
   return true;
 }
 
-// Threads per row for tiles of T rows: the butterflies of the largest-radix stage, spread over more
-// rounds when T rows of them exceed the block size that the register budget allows (0: impossible).
-constexpr int mixed_threads_per_row(int nb_min, int T, int elem_bytes) {
+// Threads per row for tiles of T rows (0: impossible).  Between three quarters of the block size that the
+// register budget allows and all of it, the count that wastes the fewest butterfly slots
+// (sum over stages of ceil(nb / tpr) * tpr / nb); ties go to the larger count.
+constexpr int mixed_threads_per_row(const MixedPlan& pl, int T, int elem_bytes) {
   const int cap = elem_bytes == 8 ? 512 : 256;
-  int tpr = nb_min;
-  for (int k = 2; T * tpr > cap && tpr > 1; ++k) tpr = (nb_min + k - 1) / k;
-  return T * tpr > cap ? 0 : tpr;
+  int hi = cap / T;
+  if (hi < 1 || pl.ns < 1) return 0;
+  int nbmax = 1;
+  for (int s = 0; s < pl.ns; ++s)
+    if (pl.st[s].nb > nbmax) nbmax = pl.st[s].nb;
+  if (hi > nbmax) hi = nbmax;
+  int lo = (3 * cap / 4 + T - 1) / T;
+  if (lo > hi) lo = hi;
+  if (lo < 1) lo = 1;
+  int best = hi;
+  long long best_cost = -1;
+  for (int tpr = hi; tpr >= lo; --tpr) {
+    long long cost = 0;
+    for (int s = 0; s < pl.ns; ++s) {
+      const int nb = pl.st[s].nb;
+      cost += (long long)((nb + tpr - 1) / tpr) * tpr * 65536 / nb;
+    }
+    if (best_cost < 0 || cost < best_cost) {
+      best_cost = cost;
+      best = tpr;
+    }
+  }
+  return best;
 }
 
 JD_HD uint32_t jd_mulhi(uint32_t a, uint32_t b) {
@@ -149,10 +191,14 @@ JD_HD void mixed_dispatch(int radix, F&& f) {
     case 3: f.template run<3>(); break;
     case 4: f.template run<4>(); break;
     case 5: f.template run<5>(); break;
+    case 6: f.template run<6>(); break;
     case 7: f.template run<7>(); break;
     case 8: f.template run<8>(); break;
+    case 10: f.template run<10>(); break;
     case 11: f.template run<11>(); break;
+    case 12: f.template run<12>(); break;
     case 13: f.template run<13>(); break;
+    case 15: f.template run<15>(); break;
     case 16: f.template run<16>(); break;
     default: break;
   }

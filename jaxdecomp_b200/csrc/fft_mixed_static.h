@@ -38,7 +38,7 @@ struct MixedCfg {
   static constexpr MixedPlan PL = mixed_plan_of(N);
   static constexpr int NS = PL.ns;
   static constexpr int PITCH = mixed_static_pitch(N, EB);
-  static constexpr int TPR = mixed_threads_per_row(PL.nb_min, T, EB);
+  static constexpr int TPR = mixed_threads_per_row(PL, T, EB);
   static constexpr int NT = (T * TPR + 31) / 32 * 32;
   static constexpr size_t SMEM = 2 * (size_t)T * PITCH * EB;
   static constexpr int MINB = SMEM * 2 + 2048 <= 227 * 1024 ? 2 : 1;
@@ -98,7 +98,7 @@ __device__ __forceinline__ void static_stage(const PassDesc& d, const cx<R>* __r
       E* p = dst + padidx(base, 1);
 #pragma unroll
       for (int q = 0; q < RADIX; ++q) p[q * (LS + LS / 8)] = a[q];
-    } else if constexpr (LS == 1 && (RADIX == 16 || RADIX == 8 || RADIX == 4 || RADIX == 2)) {
+    } else if constexpr (LS == 1 && sizeof(R) == 4 && (RADIX == 16 || RADIX == 8 || RADIX == 4 || RADIX == 2)) {
       // RADIX consecutive columns starting at a multiple of RADIX: inside one padded group of sixteen
       cx2<R>* v = reinterpret_cast<cx2<R>*>(dst + padidx(base, 1));
 #pragma unroll

@@ -1,6 +1,7 @@
 // Register-resident butterflies beyond radix 8: the 16-point DFT of the
-// specialised power-of-two kernel, prime-length DFTs (3, 5, 7, 11, 13) for the
-// mixed-radix kernel, and the in-register twiddle multiplication they share.
+// specialised power-of-two kernel, prime-length DFTs (3, 5, 7, 11, 13) and small
+// composite ones (6, 10, 12, 15) for the mixed-radix kernel, and the
+// in-register twiddle multiplication they share.
 // Only the forward direction exp(-2*pi*i*..) exists; callers obtain the
 // inverse by swapping real and imaginary parts on the way in and out.
 // The reference leaves all of this to cuFFT (src/csrc/fft.cu:72-121).
@@ -120,10 +121,77 @@ JD_HD void dft_prime(cx<R> (&a)[P]) {
   a[0] = sum;
 }
 
+template <typename R, int RADIX>
+JD_HD void dft_any(cx<R> (&a)[RADIX]);
+
+// ---- composite lengths (6, 10, 12, 15) ---------------------------------------------------------------
+// a * exp(-2 pi i NUM / DEN) with the constant folded by the compiler
+template <typename R, int NUM, int DEN>
+JD_HD cx<R> mul_root(cx<R> a) {
+  constexpr int k = NUM % DEN;
+  if constexpr (k == 0) {
+    return a;
+  } else if constexpr (4 * k == DEN) {
+    return cx<R>{a.y, -a.x};
+  } else if constexpr (2 * k == DEN) {
+    return cx<R>{-a.x, -a.y};
+  } else if constexpr (4 * k == 3 * DEN) {
+    return cx<R>{-a.y, a.x};
+  } else {
+    constexpr R c = (R)jd_sincos_2pi(k, DEN, false), s = (R)jd_sincos_2pi(k, DEN, true);
+    return cx<R>{a.x * c + a.y * s, a.y * c - a.x * s};
+  }
+}
+
+template <typename R, int A, int B, int N_, int K1>
+JD_HD void comp_twiddle(cx<R> (&t)[A]) {
+  t[K1] = mul_root<R, N_ * K1, A * B>(t[K1]);
+  if constexpr (K1 + 1 < A) comp_twiddle<R, A, B, N_, K1 + 1>(t);
+}
+
+// first layer of an (A x B)-point DFT on x[n + B m]: A-point DFTs over m for column n, then W_AB^(n k1)
+template <typename R, int A, int B, int N_>
+JD_HD void comp_columns(cx<R> (&a)[A * B]) {
+  cx<R> t[A];
+#pragma unroll
+  for (int m = 0; m < A; ++m) t[m] = a[N_ + B * m];
+  dft_any<R, A>(t);
+  if constexpr (N_ > 0) comp_twiddle<R, A, B, N_, 1>(t);
+#pragma unroll
+  for (int k1 = 0; k1 < A; ++k1) a[N_ + B * k1] = t[k1];
+  if constexpr (N_ + 1 < B) comp_columns<R, A, B, N_ + 1>(a);
+}
+
+// X[k1 + A k2] = sum_n W_B^(n k2) W_AB^(n k1) sum_m x[n + B m] W_A^(m k1)
+template <typename R, int A, int B>
+JD_HD void dft_composite(cx<R> (&a)[A * B]) {
+  comp_columns<R, A, B, 0>(a);
+  cx<R> out[A * B];
+#pragma unroll
+  for (int k1 = 0; k1 < A; ++k1) {
+    cx<R> t[B];
+#pragma unroll
+    for (int n = 0; n < B; ++n) t[n] = a[n + B * k1];
+    dft_any<R, B>(t);
+#pragma unroll
+    for (int k2 = 0; k2 < B; ++k2) out[k1 + A * k2] = t[k2];
+  }
+#pragma unroll
+  for (int k = 0; k < A * B; ++k) a[k] = out[k];
+}
+
 // DFT of RADIX values held in registers, natural order in and out
 template <typename R, int RADIX>
 JD_HD void dft_any(cx<R> (&a)[RADIX]) {
-  if constexpr (RADIX == 2) {
+  if constexpr (RADIX == 6) {
+    dft_composite<R, 2, 3>(a);
+  } else if constexpr (RADIX == 10) {
+    dft_composite<R, 2, 5>(a);
+  } else if constexpr (RADIX == 12) {
+    dft_composite<R, 4, 3>(a);
+  } else if constexpr (RADIX == 15) {
+    dft_composite<R, 3, 5>(a);
+  } else if constexpr (RADIX == 2) {
     dft2(a[0], a[1]);
   } else if constexpr (RADIX == 4) {
     dft4(a[0], a[1], a[2], a[3]);

@@ -109,7 +109,8 @@ def test_invalid_descriptor_is_rejected():
 
 
 @pytest.mark.parametrize("n", [64, 128, 256, 512, 1024, 2048, 4096, 100, 384,
-                               2, 4, 6, 12, 30, 77, 143, 768, 1000, 1365, 1536, 2310, 34, 97])
+                               2, 4, 6, 12, 30, 77, 143, 768, 1000, 1365, 1536, 2310, 34, 97,
+                               96, 160, 240, 288, 480])
 @pytest.mark.parametrize("dtype", [torch.complex64, torch.complex128])
 def test_row_transforms_all_stage_structures(n, dtype):
     """Every radix structure (8.8.2, 8.8.4, 8.8.8, ...) with intra-row padding, mixed-radix lengths
