@@ -83,6 +83,8 @@ PYBIND11_MODULE(_jdb200, m) {
                     [](PassDesc& d, uintptr_t v) { d.in = P(v); })
       .def_property("twiddle", [](const PassDesc& d) { return (uintptr_t)d.twiddle; },
                     [](PassDesc& d, uintptr_t v) { d.twiddle = P(v); })
+      .def_property("tw_stage", [](const PassDesc& d) { return (uintptr_t)d.tw_stage; },
+                    [](PassDesc& d, uintptr_t v) { d.tw_stage = P(v); })
       .def_property("chirp", [](const PassDesc& d) { return (uintptr_t)d.chirp; },
                     [](PassDesc& d, uintptr_t v) { d.chirp = P(v); })
       .def_property("bhat", [](const PassDesc& d) { return (uintptr_t)d.bhat; },
@@ -103,7 +105,7 @@ PYBIND11_MODULE(_jdb200, m) {
   m.def("pass_smem_bytes", &pass_smem_bytes);
   m.def("get_fft_tables", [](int C, int M, int elem_bytes, bool device) {
     FftTables t = get_fft_tables(C, M, elem_bytes, device);
-    return py::make_tuple((uintptr_t)t.twiddle, (uintptr_t)t.chirp, (uintptr_t)t.bhat);
+    return py::make_tuple((uintptr_t)t.twiddle, (uintptr_t)t.chirp, (uintptr_t)t.bhat, (uintptr_t)t.tw_stage);
   });
   m.def("clear_fft_tables", &clear_fft_tables);
 

@@ -16,9 +16,9 @@
 //   * the butterflies of a pencil are owned by a fixed group of M/16 threads,
 //     which synchronise among themselves with a named barrier (or __syncwarp
 //     when the group fits in a warp) instead of a block-wide barrier;
-//   * per butterfly only the factors w, w^2, w^4 (w^8) are read from the table of
-//     M roots; the other powers are products of those (the FP pipe has head-room,
-//     the load pipe has not);
+//   * per butterfly only the factors w, w^2, w^4 (w^8) are read, as one contiguous
+//     record of a per-stage table; the other powers are products of those (the
+//     FP pipe has head-room, the load pipe has not);
 //   * a plain (non-rotating) pass writes the last stage's results directly to
 //     global memory; a rotating pass goes through shared memory once more so
 //     that each thread stores 16 contiguous bytes along the destination's
@@ -38,31 +38,14 @@
 
 #include <cstdlib>
 
+#include "fft_fast_plan.h"
 #include "fft_radix.h"
 #include "launch.h"
 #include "tile_ops.h"
 
 namespace jdb {
 
-// ---- stage plan ---------------------------------------------------------------------------------------------------
-// log2 of the radix of stage s for M = 2^logm (7 <= logm <= 12)
-__host__ __device__ constexpr int plan_radix_log(int logm, int s) {
-  switch (logm) {
-    case 7: return s == 0 ? 4 : 3;
-    case 8: return 4;
-    case 9: return 3;
-    case 10: return s == 0 ? 4 : 3;
-    case 11: return s < 2 ? 4 : 3;
-    default: return 4;  // 12
-  }
-}
-__host__ __device__ constexpr int plan_num_stages(int logm) { return logm <= 8 ? 2 : 3; }
-// log2 of Ls (length of the finished sub-transforms) before stage s
-__host__ __device__ constexpr int plan_log_ls(int logm, int s) {
-  int l = 0;
-  for (int i = 0; i < s; ++i) l += plan_radix_log(logm, i);
-  return l;
-}
+// ---- stage plan: fft_fast_plan.h ----------------------------------------------------------------------------------
 template <typename R, int LOGM_, int LOGT_, bool STORE_T_>
 struct FastCfg {
   static constexpr int LOGM = LOGM_, LOGT = LOGT_;
@@ -103,13 +86,31 @@ __device__ __forceinline__ cx<R> ldg_cx(const cx<R>* p) {
   }
 }
 
-// a[FIRST + STRIDE*q] *= w^q for q = 1..N-1 (N = 8 or 16), where w^(2^i) are read from the table of M roots
-// (tw[n] = exp(-2 pi i n / M), `idx` = index of w) and the other powers are products of at most four of them.
-// The kernel is limited by the L1/shared-memory data pipe, so deriving twiddles on the FP pipe is cheaper
-// than loading a full row of factors per butterfly.
+// a[FIRST + STRIDE*q] *= w^q for q = 1..N-1 (N = 8 or 16).  `rec` is the stage's record for this
+// butterfly, {w, w^2, w^4, w^8} (fft_fast_plan.h), read with 16-byte loads; the other powers are
+// products of at most four of them.  The kernel is limited by the L1/shared-memory data pipe, so
+// deriving twiddles on the FP pipe is cheaper than loading a full row of factors per butterfly, and
+// contiguous records are cheaper than scattered reads of the table of M roots.
 template <typename R, int N, int FIRST, int STRIDE>
-__device__ __forceinline__ void apply_tw(const cx<R>* __restrict__ tw, int idx, cx<R> (&a)[16]) {
-  const cx<R> w1 = ldg_cx<R>(tw + idx), w2 = ldg_cx<R>(tw + 2 * idx), w4 = ldg_cx<R>(tw + 4 * idx);
+__device__ __forceinline__ void apply_tw(const cx<R>* __restrict__ rec, cx<R> (&a)[16]) {
+  cx<R> w1, w2, w4, w8;
+  if constexpr (sizeof(R) == 4) {
+    const float4 lo = __ldg(reinterpret_cast<const float4*>(rec));
+    w1 = cx<R>{lo.x, lo.y};
+    w2 = cx<R>{lo.z, lo.w};
+    if constexpr (N == 16) {
+      const float4 hi = __ldg(reinterpret_cast<const float4*>(rec) + 1);
+      w4 = cx<R>{hi.x, hi.y};
+      w8 = cx<R>{hi.z, hi.w};
+    } else {
+      w4 = ldg_cx<R>(rec + 2);
+    }
+  } else {
+    w1 = ldg_cx<R>(rec);
+    w2 = ldg_cx<R>(rec + 1);
+    w4 = ldg_cx<R>(rec + 2);
+    if constexpr (N == 16) w8 = ldg_cx<R>(rec + 3);
+  }
   const cx<R> w3 = cmul(w1, w2), w5 = cmul(w1, w4), w6 = cmul(w2, w4), w7 = cmul(w3, w4);
   a[FIRST + STRIDE * 1] = cmul(a[FIRST + STRIDE * 1], w1);
   a[FIRST + STRIDE * 2] = cmul(a[FIRST + STRIDE * 2], w2);
@@ -119,7 +120,6 @@ __device__ __forceinline__ void apply_tw(const cx<R>* __restrict__ tw, int idx, 
   a[FIRST + STRIDE * 6] = cmul(a[FIRST + STRIDE * 6], w6);
   a[FIRST + STRIDE * 7] = cmul(a[FIRST + STRIDE * 7], w7);
   if constexpr (N == 16) {
-    const cx<R> w8 = ldg_cx<R>(tw + 8 * idx);
     a[FIRST + STRIDE * 8] = cmul(a[FIRST + STRIDE * 8], w8);
     a[FIRST + STRIDE * 9] = cmul(a[FIRST + STRIDE * 9], cmul(w1, w8));
     a[FIRST + STRIDE * 10] = cmul(a[FIRST + STRIDE * 10], cmul(w2, w8));
@@ -155,7 +155,7 @@ __device__ __forceinline__ void fast_stage(cx<R>* rowp, int j, int sgroup, cx<R>
   }
   if constexpr (RL == 4) {
     const int kk = j & (Ls - 1);
-    if constexpr (S > 0) apply_tw<R, 16, 0, 1>(stw, kk << (LOGM - LOGLS - 4), a);
+    if constexpr (S > 0) apply_tw<R, 16, 0, 1>(stw + 4 * (plan_stage_record0(LOGM, S) + kk), a);
     dft16<R>(a);
     if (to_smem) {
       const int base = ((j - kk) << 4) + kk;
@@ -179,8 +179,8 @@ __device__ __forceinline__ void fast_stage(cx<R>* rowp, int j, int sgroup, cx<R>
       const int bf = j + m * Q;
       const int kk = bf & (Ls - 1);
       if constexpr (S > 0) {
-        if (m == 0) apply_tw<R, 8, 0, 2>(stw, kk << (LOGM - LOGLS - 3), a);
-        else apply_tw<R, 8, 1, 2>(stw, kk << (LOGM - LOGLS - 3), a);
+        if (m == 0) apply_tw<R, 8, 0, 2>(stw + 4 * (plan_stage_record0(LOGM, S) + kk), a);
+        else apply_tw<R, 8, 1, 2>(stw + 4 * (plan_stage_record0(LOGM, S) + kk), a);
       }
       E x[8];
 #pragma unroll
@@ -245,7 +245,7 @@ __global__ void __launch_bounds__((FastCfg<R, LOGM, LOGT, STORE_T>::NT), (FastCf
 #pragma unroll
     for (int k = 0; k < 16; ++k) a[k] = cswap(a[k]);
   }
-  const E* __restrict__ stw = (const E*)d.twiddle;  // M roots of unity
+  const E* __restrict__ stw = (const E*)d.tw_stage;  // per-stage twiddle records
   fast_stage<Cfg, R, 0>(rowp, j, tid / Cfg::GS, a, stw, Cfg::NS > 1 || STORE_T);
 
   const R scale = (R)d.scale;
@@ -341,7 +341,7 @@ int fast_pass_logT(int logM, int elem_bytes, bool big) {
 }
 
 bool fast_pass_eligible(const PassDesc& d) {
-  if (d.fft_mode != JD_FFT_POW2) return false;
+  if (d.fft_mode != JD_FFT_POW2 || d.tw_stage == nullptr) return false;
   if (d.elem_bytes != 8 && d.elem_bytes != 16) return false;
   if (d.M < (d.elem_bytes == 8 ? 128 : 256) || d.M > (d.elem_bytes == 8 ? 4096 : 2048) || d.C != d.M) return false;
   if (d.load_t_contig || d.is_c != 1) return false;

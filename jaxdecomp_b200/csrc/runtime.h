@@ -22,6 +22,7 @@ namespace jdb {
 
 struct FftTables {
   const void* twiddle = nullptr;
+  const void* tw_stage = nullptr;
   const void* chirp = nullptr;
   const void* bhat = nullptr;
 };

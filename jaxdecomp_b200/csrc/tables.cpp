@@ -1,6 +1,7 @@
 // Constant tables for the FFT kernels, computed once on the host in extended
 // precision and cached per (length, element size, memory space):
 //   twiddle[n] = exp(-2*pi*i*n/M), n < M
+//   tw_stage   = per-stage records {w, w^2, w^4, w^8} of the specialised power-of-two kernel (fft_fast_plan.h)
 //   chirp[n]   = exp(-i*pi*n^2/C), n < C                      (Bluestein)
 //   bhat[m]    = FFT_M(b)[m] / M with b[m] = b[M-m] = conj(chirp[m]), m < C   (Bluestein)
 // The reference keeps cuFFT plans in its descriptor manager for the same
@@ -17,6 +18,7 @@
 #include <tuple>
 #include <vector>
 
+#include "fft_fast_plan.h"
 #include "runtime.h"
 
 namespace jdb {
@@ -77,6 +79,7 @@ static void* upload(const std::vector<cld>& v, int elem_bytes, bool device) {
 
 struct TableSet {
   void* twiddle = nullptr;
+  void* tw_stage = nullptr;
   void* chirp = nullptr;
   void* bhat = nullptr;
   bool device = false;
@@ -102,6 +105,22 @@ FftTables get_fft_tables(int C, int M, int elem_bytes, bool device) {
       tw[n] = cld(cosl(ang), sinl(ang));
     }
     ts.twiddle = upload(tw, elem_bytes, device);
+    int logm = 0;
+    while ((1 << logm) < M) ++logm;
+    if (C == M && (1 << logm) == M && logm >= kFastMinLog && logm <= kFastMaxLog) {
+      // records {w, w^2, w^4, w^8} per stage >= 1 and kk < Ls, w = exp(-2 pi i kk / (Ls * radix))
+      std::vector<cld> rec((size_t)plan_stage_records(logm) * 4);
+      for (int s = 1; s < plan_num_stages(logm); ++s) {
+        const int ls = 1 << plan_log_ls(logm, s);
+        const int span = ls << plan_radix_log(logm, s);
+        for (int kk = 0; kk < ls; ++kk)
+          for (int p = 0; p < 4; ++p) {
+            const long double ang = -2.0L * kPi * (long double)(kk << p) / (long double)span;
+            rec[((size_t)plan_stage_record0(logm, s) + kk) * 4 + p] = cld(cosl(ang), sinl(ang));
+          }
+      }
+      ts.tw_stage = upload(rec, elem_bytes, device);
+    }
     if (C != M) {
       if (M < 2 * C - 1) throw std::runtime_error("tables: Bluestein length too short");
       std::vector<cld> chirp(C), b(M, cld(0, 0));
@@ -123,6 +142,7 @@ FftTables get_fft_tables(int C, int M, int elem_bytes, bool device) {
   }
   FftTables out;
   out.twiddle = it->second.twiddle;
+  out.tw_stage = it->second.tw_stage;
   out.chirp = it->second.chirp;
   out.bhat = it->second.bhat;
   return out;
@@ -132,7 +152,7 @@ void clear_fft_tables() {
   std::lock_guard<std::mutex> lk(g_mu);
   for (auto& kv : g_tables) {
     TableSet& ts = kv.second;
-    for (void* p : {ts.twiddle, ts.chirp, ts.bhat}) {
+    for (void* p : {ts.twiddle, ts.tw_stage, ts.chirp, ts.bhat}) {
       if (!p) continue;
       if (ts.device)
         cudaFree(p);

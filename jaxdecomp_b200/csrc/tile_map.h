@@ -68,6 +68,7 @@ struct PassDesc {
   const void* in;
   void* out[JD_MAX_PEERS];
   const void* twiddle;    // M entries: exp(-2*pi*i*n/M)
+  const void* tw_stage;   // per-stage twiddle records of the specialised power-of-two kernel (fft_fast_plan.h), or null
   const void* chirp;      // Bluestein: C entries exp(-i*pi*n^2/C)
   const void* bhat;       // Bluestein: M entries FFT_M(conj chirp, wrapped) / M
   const void* mul;        // optional pointwise multiplier

@@ -336,6 +336,6 @@ def fill_desc(native, spec: PassSpec, elem_bytes: int, inverse: bool, scale: flo
     for k, v in tl.items():
         setattr(d, k, v)
     if spec.fft:
-        tw, ch, bh = native.get_fft_tables(C, tl["M"], elem_bytes, device_tables)
-        d.twiddle, d.chirp, d.bhat = tw, ch, bh
+        tw, ch, bh, tws = native.get_fft_tables(C, tl["M"], elem_bytes, device_tables)
+        d.twiddle, d.chirp, d.bhat, d.tw_stage = tw, ch, bh, tws
     return d
