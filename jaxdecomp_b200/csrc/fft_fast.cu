@@ -19,10 +19,13 @@
 //   * per butterfly only the factors w, w^2, w^4 (w^8) are read, as one contiguous
 //     record of a per-stage table; the other powers are products of those (the
 //     FP pipe has head-room, the load pipe has not);
-//   * a plain (non-rotating) pass writes the last stage's results directly to
-//     global memory; a rotating pass goes through shared memory once more so
-//     that each thread stores 16 contiguous bytes along the destination's
-//     fastest axis, into the buffer of the peer that owns those columns;
+//   * both kinds of pass write the last stage's results directly from registers
+//     to global memory.  In a rotating pass the threads are re-assigned for the
+//     last stage so that neighbouring lanes hold the same column of neighbouring
+//     rows: their stores form runs of T elements along the destination's fastest
+//     axis, in the buffer of the peer that owns those columns.  (An earlier
+//     version transposed through shared memory once more; that exchange cost a
+//     third of the shared-memory traffic of the pass.);
 //   * measured on B200, stores in runs shorter than 128 bytes reach only a
 //     fraction of the NVLink (64-byte runs: 479 of 715 GB/s) and HBM (64-byte
 //     runs: 3.2 of 6.2 TB/s) write bandwidth, so passes whose stores cross
@@ -57,7 +60,12 @@ struct FastCfg {
   // threads that synchronise together: whole rows, and at most eight groups per block (named barriers 1..8)
   static constexpr int GS = UPR > NT / 8 ? UPR : NT / 8;
   static constexpr int ROWLEN = M + M / 8;
-  static constexpr int PITCH = ROWLEN + 2;     // == 2 (mod 16): conflict-free transposed reads for 4 row pairs
+  // Rotating passes: the last stage is done by threads laid out across the rows (see last_stage_map);
+  // sixteen consecutive threads then read RH = min(T, 8) rows x 16/RH columns, which fall into
+  // sixteen different 8-byte bank pairs when the pitch is 16/RH (mod 16).
+  static constexpr int RH = T < 8 ? T : 8;
+  static constexpr int CB = 16 / RH;
+  static constexpr int PITCH = ROWLEN + CB;
   static constexpr int NS = plan_num_stages(LOGM);
   static constexpr int REGS = sizeof(R) == 8 ? 128 : 64;
   static constexpr int MINB_ = 65536 / (NT * REGS);
@@ -131,10 +139,23 @@ __device__ __forceinline__ void apply_tw(const cx<R>* __restrict__ rec, cx<R> (&
   }
 }
 
+// Thread layout of the last stage of a rotating pass: consecutive threads own consecutive rows of the
+// same butterfly index, so that the results of one column, which are contiguous in the destination,
+// are stored by neighbouring lanes straight from registers (runs of T elements).
+template <typename Cfg>
+__device__ __forceinline__ void last_stage_map(int tid, int& row, int& j) {
+  const int r_lo = tid % Cfg::RH;
+  const int b = (tid / Cfg::RH) % Cfg::CB;
+  const int rest = tid / 16;
+  constexpr int RG = Cfg::T / Cfg::RH;  // groups of RH rows
+  row = r_lo + Cfg::RH * (rest % RG);
+  j = Cfg::CB * (rest / RG) + b;
+}
+
 // One stage on the sixteen values a[k] = row[j + k*M/16] of a thread.
 template <typename Cfg, typename R, int S>
-__device__ __forceinline__ void fast_stage(cx<R>* rowp, int j, int sgroup, cx<R> (&a)[16], const cx<R>* __restrict__ stw,
-                                           bool to_smem) {
+__device__ __forceinline__ void fast_stage(cx<R>* sm, cx<R>* rowp, int j, int sgroup, cx<R> (&a)[16],
+                                           const cx<R>* __restrict__ stw, bool to_smem) {
   using E = cx<R>;
   constexpr int LOGM = Cfg::LOGM;
   constexpr int RL = plan_radix_log(LOGM, S);
@@ -151,7 +172,8 @@ __device__ __forceinline__ void fast_stage(cx<R>* rowp, int j, int sgroup, cx<R>
 #pragma unroll
       for (int k = 0; k < 16; ++k) a[k] = rowp[padidx(j + k * Q, 1)];
     }
-    group_sync<Cfg::UPR, Cfg::GS>(sgroup);  // all reads of the group done before anyone overwrites
+    // all reads of the group done before anyone overwrites (the last stage of a rotating pass writes nothing)
+    if constexpr (!(Cfg::STORE_T && S + 1 == Cfg::NS)) group_sync<Cfg::UPR, Cfg::GS>(sgroup);
   }
   if constexpr (RL == 4) {
     const int kk = j & (Ls - 1);
@@ -209,8 +231,16 @@ __device__ __forceinline__ void fast_stage(cx<R>* rowp, int j, int sgroup, cx<R>
     }
   }
   if constexpr (S + 1 < Cfg::NS) {
-    group_sync<Cfg::UPR, Cfg::GS>(sgroup);  // this stage's writes visible to the group
-    fast_stage<Cfg, R, S + 1>(rowp, j, sgroup, a, stw, (S + 2 < Cfg::NS) || Cfg::STORE_T);
+    if constexpr (Cfg::STORE_T && S + 2 == Cfg::NS) {
+      // the last stage of a rotating pass reads rows written by other thread groups
+      __syncthreads();
+      int row2, j2;
+      last_stage_map<Cfg>(threadIdx.x, row2, j2);
+      fast_stage<Cfg, R, S + 1>(sm, sm + row2 * Cfg::PITCH, j2, sgroup, a, stw, false);
+    } else {
+      group_sync<Cfg::UPR, Cfg::GS>(sgroup);  // this stage's writes visible to the group
+      fast_stage<Cfg, R, S + 1>(sm, rowp, j, sgroup, a, stw, S + 2 < Cfg::NS);
+    }
   }
 }
 
@@ -246,7 +276,7 @@ __global__ void __launch_bounds__((FastCfg<R, LOGM, LOGT, STORE_T>::NT), (FastCf
     for (int k = 0; k < 16; ++k) a[k] = cswap(a[k]);
   }
   const E* __restrict__ stw = (const E*)d.tw_stage;  // per-stage twiddle records
-  fast_stage<Cfg, R, 0>(rowp, j, tid / Cfg::GS, a, stw, Cfg::NS > 1 || STORE_T);
+  fast_stage<Cfg, R, 0>(sm, rowp, j, tid / Cfg::GS, a, stw, Cfg::NS > 1);
 
   const R scale = (R)d.scale;
   const bool do_scale = d.scale != 1.0;
@@ -266,51 +296,27 @@ __global__ void __launch_bounds__((FastCfg<R, LOGM, LOGT, STORE_T>::NT), (FastCf
       ((E*)d.out[ob.peer + pc + pt])[toff + (c - pc * d.Cl)] = v;
     }
   } else {
-    __syncthreads();  // the transposed store reads every row of the tile
-    constexpr int PER16 = 16 / (2 * (int)sizeof(R));  // elements per 16-byte store: 2 (complex64) or 1 (complex128)
-    constexpr int TP = T / PER16;                    // threads that share one column
-    constexpr int LOGTP = LOGT - (PER16 == 2 ? 1 : 0);
-    constexpr int STEP = NT / TP;                    // columns advanced per iteration
-    static_assert(STEP % 16 == 0, "column step must keep the padded index linear");
-    constexpr int STEPP = STEP + STEP / 8;
-    // Thread -> (row pair tp, column cs).  Sixteen consecutive threads always cover four row pairs x
-    // four columns: with PITCH == 2 (mod 16) their 8-byte reads then fall into sixteen different banks.
-    int tp, cs;
-    if constexpr (TP >= 8) {
-      const int rest = tid >> 4;
-      tp = (tid & 3) + 4 * (rest & (TP / 4 - 1));
-      cs = ((tid >> 2) & 3) + 4 * (rest / (TP / 4));
-    } else {
-      tp = tid & (TP - 1);
-      cs = tid >> LOGTP;
-    }
-    const int t = tp * PER16;
+    // a[k] now is the result for column j2 + k*M/16 of row row2 (layout of last_stage_map): lanes that
+    // hold the same column store neighbouring elements of the destination's fastest axis.
+    int row2, j2;
+    last_stage_map<Cfg>(tid, row2, j2);
     const OutBase ob = out_base_for(d, o, b);
-    const int tg = t0 + t;
+    const int tg = t0 + row2;
     const int pt = d.split_axis == 2 ? tg / d.Tl : 0;
     const long long toff = ob.off + (long long)(tg - pt * d.Tl) * d.os_t;
-    const E* src = sm + t * Cfg::PITCH + padidx(cs, 1);
     const int logCl = 31 - __clz(d.Cl);
-#pragma unroll 4
-    for (int i = 0; i < M / STEP; ++i) {
-      const int c = cs + i * STEP;
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      const int c = j2 + k * UPR;
       int pc = 0, cl = c;
       if (d.split_axis == 1) {
         pc = c >> logCl;
         cl = c & (d.Cl - 1);
       }
-      E* dst = (E*)d.out[ob.peer + pc + pt] + (toff + (long long)cl * d.os_c);
-      E v0 = src[i * STEPP];
-      if (inv) v0 = cswap(v0);
-      if (do_scale) v0 = cscale(v0, scale);
-      if constexpr (PER16 == 2) {
-        E v1 = src[Cfg::PITCH + i * STEPP];
-        if (inv) v1 = cswap(v1);
-        if (do_scale) v1 = cscale(v1, scale);
-        *reinterpret_cast<cx2<R>*>(dst) = cx2<R>{v0, v1};
-      } else {
-        *dst = v0;
-      }
+      E v = a[k];
+      if (inv) v = cswap(v);
+      if (do_scale) v = cscale(v, scale);
+      ((E*)d.out[ob.peer + pc + pt])[toff + (long long)cl * d.os_c] = v;
     }
   }
 }
@@ -352,12 +358,6 @@ bool fast_pass_eligible(const PassDesc& d) {
   if (d.Tn % (1 << lt)) return false;
   if (d.store_t_contig) {
     if (d.os_t != 1) return false;
-    const int per16 = 16 / d.elem_bytes;
-    if (per16 == 2) {
-      if ((d.Tl & 1) || (d.out_base & 1) || (d.os_c & 1) || (d.os_o & 1) || (d.os_b & 1)) return false;
-      for (int p = 0; p < d.npeers; ++p)
-        if ((uintptr_t)d.out[p] % 16) return false;
-    }
     if (d.split_axis == 1 && !is_pow2(d.Cl)) return false;
   } else {
     if (d.os_c != 1) return false;
