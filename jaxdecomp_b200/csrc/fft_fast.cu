@@ -331,8 +331,8 @@ static bool big_tiles(const PassDesc& d) {
   const char* env = std::getenv("JD_B200_BIGTILE");
   if (env && *env) return env[0] != '0';
   if (!d.store_t_contig) return false;
-  // local rotating passes: measured 3 % faster with large tiles at 1024 points, slower at 512 and below
-  return d.npeers > 1 || d.M == 1024;
+  // local rotating passes: measured 1-2 % slower with large tiles at every length
+  return d.npeers > 1;
 }
 
 int fast_pass_logT(int logM, int elem_bytes, bool big) {
