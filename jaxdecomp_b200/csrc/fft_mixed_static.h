@@ -1,6 +1,6 @@
 // Mixed-radix tile pass specialised on the transform length: same algorithm
 // and data path as fft_mixed.cu (first stage from global memory, ping-pong
-// stages in shared memory, direct or transposed store), but the stage plan,
+// stages in shared memory, stores straight from the registers of the last stage), but the stage plan,
 // the tile height, the row pitch and the thread layout are compile-time
 // constants, so the per-element index arithmetic (the limiter of the generic
 // kernel: 146 instructions per element, two thirds of them integer) folds
@@ -16,18 +16,24 @@
 namespace jdb {
 
 // Geometry rules; ops/passes.py::choose_tiling applies the same ones, and the launcher falls back to
-// the generic kernel when a descriptor was tiled differently.
-constexpr int mixed_static_pitch(int n, int elem_bytes) {
-  const int rowlen = n + 2 * ((n + 15) / 16);
-  return elem_bytes == 8 ? rowlen + (((2 - rowlen) % 16) + 16) % 16 : rowlen + (((1 - rowlen) % 8) + 8) % 8;
-}
+// the generic kernel when a descriptor was tiled differently.  The tile height follows from the shared-memory
+// budget with the pitch of tall tiles; the final pitch then makes the reads of the last stage of a rotating
+// pass conflict-free: the threads of one shared-memory wavefront (16 lanes of 8-byte elements, 8 lanes of
+// 16-byte ones) cover RH = min(T, 8) rows x CB columns, which needs pitch == CB modulo the wavefront width.
+constexpr int mixed_rowlen(int n) { return n + 2 * ((n + 15) / 16); }
+constexpr int mixed_pitch_mod(int rowlen, int want, int mod) { return rowlen + (((want - rowlen) % mod) + mod) % mod; }
 constexpr int mixed_static_T(int n, int elem_bytes, bool store_t) {
-  const int pitch = mixed_static_pitch(n, elem_bytes);
+  const int pitch = elem_bytes == 8 ? mixed_pitch_mod(mixed_rowlen(n), 2, 16) : mixed_pitch_mod(mixed_rowlen(n), 1, 8);
   int T = 1;
   while (T < 32 && 2 * (2 * T) * pitch * elem_bytes <= 110 * 1024) T *= 2;
   if (store_t)
     while (T * elem_bytes < 64 && 2 * (2 * T) * pitch * elem_bytes <= 220 * 1024) T *= 2;
   return T;
+}
+constexpr int mixed_static_pitch(int n, int elem_bytes, int T) {
+  const int lanes = elem_bytes == 8 ? 16 : 8;
+  const int rh = T < 8 ? T : 8;
+  return mixed_pitch_mod(mixed_rowlen(n), lanes / rh, lanes);
 }
 
 template <typename R, int N_, int T_, bool DOUT_>
@@ -37,18 +43,21 @@ struct MixedCfg {
   static constexpr int EB = 2 * (int)sizeof(R);
   static constexpr MixedPlan PL = mixed_plan_of(N);
   static constexpr int NS = PL.ns;
-  static constexpr int PITCH = mixed_static_pitch(N, EB);
+  static constexpr int PITCH = mixed_static_pitch(N, EB, T);
+  static constexpr int RH = T < 8 ? T : 8;                 // rows per shared-memory wavefront in the last rotating stage
+  static constexpr int CB = (EB == 8 ? 16 : 8) / RH;       // columns per wavefront
   static constexpr int TPR = mixed_threads_per_row(PL, T, EB);
   static constexpr int NT = (T * TPR + 31) / 32 * 32;
   static constexpr size_t SMEM = 2 * (size_t)T * PITCH * EB;
   static constexpr int MINB = SMEM * 2 + 2048 <= 227 * 1024 ? 2 : 1;
-  static_assert(NS > 0 && TPR > 0, "length not supported by the mixed-radix plan");
+  static_assert(NS >= 2 && TPR > 0, "length not supported by the specialised mixed-radix kernel");
   static_assert(SMEM <= 226 * 1024, "tile exceeds shared memory");
 };
 
 // Stage S of the plan on the butterflies of one thread.  SG: inputs come from global memory; DG: outputs go
-// to global memory.
-template <typename Cfg, typename R, int S, bool SG, bool DG>
+// to global memory, along the row (ROT false: column c at toff + c) or transposed (ROT true: column c at
+// toff + c * os_c, toff being the position of this thread's row on the destination's fastest axis).
+template <typename Cfg, typename R, int S, bool SG, bool DG, bool ROT>
 __device__ __forceinline__ void static_stage(const PassDesc& d, const cx<R>* __restrict__ tw, const cx<R>* src, cx<R>* dst,
                                              const cx<R>* __restrict__ gsrc, int j, bool inv, bool do_scale, R scale,
                                              int peer0, long long toff) {
@@ -85,14 +94,21 @@ __device__ __forceinline__ void static_stage(const PassDesc& d, const cx<R>* __r
     dft_any<R, RADIX>(a);
     const int base = blk * (LS * RADIX) + kk;
     if constexpr (DG) {
+      // c / Cl by multiply-high (c, Cl < 2^16; Cl >= 2 whenever the columns are split)
+      const uint32_t clm = d.split_axis == 1 ? (uint32_t)(0x100000000ULL / (unsigned)d.Cl) + 1u : 0u;
 #pragma unroll
       for (int q = 0; q < RADIX; ++q) {
         const int c = base + q * LS;
         E v = a[q];
         if (inv) v = cswap(v);
         if (do_scale) v = cscale(v, scale);
-        const int pc = d.split_axis == 1 ? c / d.Cl : 0;
-        ((E*)d.out[peer0 + pc])[toff + (c - pc * d.Cl)] = v;
+        const int pc = d.split_axis == 1 ? (int)__umulhi((uint32_t)c, clm) : 0;
+        const int cl = c - pc * d.Cl;
+        if constexpr (ROT) {
+          ((E*)d.out[peer0 + pc])[toff + (long long)cl * d.os_c] = v;
+        } else {
+          ((E*)d.out[peer0 + pc])[toff + cl] = v;
+        }
       }
     } else if constexpr (LS % 16 == 0) {
       E* p = dst + padidx(base, 1);
@@ -110,67 +126,32 @@ __device__ __forceinline__ void static_stage(const PassDesc& d, const cx<R>* __r
   }
 }
 
+// Which row and which butterflies a thread serves, and where that row lands in the destination.
+struct MixedThreadMap {
+  int row, j;
+  bool active;
+  int peer0;
+  long long toff;
+};
+
 template <typename Cfg, typename R, int S>
 __device__ __forceinline__ void static_stages(const PassDesc& d, const cx<R>* tw, cx<R>* buf0, cx<R>* buf1,
-                                              const cx<R>* gsrc, int row, int j, bool active, bool inv, bool do_scale,
-                                              R scale, int peer0, long long toff) {
+                                              const cx<R>* gsrc, const MixedThreadMap& m, const MixedThreadMap& mlast,
+                                              bool inv, bool do_scale, R scale) {
   using E = cx<R>;
   constexpr bool SG = S == 0;
-  constexpr bool DG = Cfg::DOUT && S == Cfg::NS - 1;
+  constexpr bool LAST = S == Cfg::NS - 1;
+  constexpr bool ROT = LAST && !Cfg::DOUT;  // last stage of a rotating pass: transposed store from registers
+  constexpr bool DG = LAST;
+  const MixedThreadMap& mm = ROT ? mlast : m;
   // stage 0 writes buffer 0, stage 1 reads it and writes buffer 1, ...
-  const E* src = ((S - 1) % 2 == 0 ? buf0 : buf1) + row * Cfg::PITCH;
-  E* dst = (S % 2 == 0 ? buf0 : buf1) + row * Cfg::PITCH;
-  if (active) static_stage<Cfg, R, S, SG, DG>(d, tw, src, dst, gsrc, j, inv, do_scale, scale, peer0, toff);
-  if constexpr (!DG) __syncthreads();
-  if constexpr (S + 1 < Cfg::NS)
-    static_stages<Cfg, R, S + 1>(d, tw, buf0, buf1, gsrc, row, j, active, inv, do_scale, scale, peer0, toff);
-}
-
-// Transposed store of the finished tile: every thread writes 16 contiguous bytes along the destination's
-// fastest axis (two rows of one column for complex64, one element for complex128).
-template <typename Cfg, typename R>
-__device__ __forceinline__ void static_rot_store(const PassDesc& d, const cx<R>* res, int o, int t0, int b, bool inv,
-                                                 bool do_scale, R scale) {
-  using E = cx<R>;
-  constexpr int PER16 = 16 / Cfg::EB;
-  constexpr int TP = Cfg::T / PER16 < 1 ? 1 : Cfg::T / PER16;  // threads that share one column
-  constexpr int CSTEP = Cfg::NT / TP;                          // columns advanced per iteration
-  const int tid = threadIdx.x;
-  const int tp = tid % TP;
-  const int cs = tid / TP;
-  const int t = tp * (Cfg::T >= PER16 ? PER16 : 1);
-  const int tg = t0 + t;
-  if (tg >= d.Tn) return;
-  const OutBase ob = out_base_for(d, o, b);
-  const int pt = d.split_axis == 2 ? tg / d.Tl : 0;
-  const long long toff = ob.off + (long long)(tg - pt * d.Tl) * d.os_t;
-  const E* src = res + t * Cfg::PITCH;
-  int pc = 0, cl = cs;
-  if (d.split_axis == 1) {
-    pc = cs / d.Cl;
-    cl = cs - pc * d.Cl;
-  }
-#pragma unroll 4
-  for (int c = cs; c < Cfg::N; c += CSTEP) {
-    E* dst = (E*)d.out[ob.peer + pc + pt] + (toff + (long long)cl * d.os_c);
-    const int col = padidx(c, 1);
-    E v0 = src[col];
-    if (inv) v0 = cswap(v0);
-    if (do_scale) v0 = cscale(v0, scale);
-    if constexpr (PER16 == 2 && Cfg::T >= 2) {
-      E v1 = src[Cfg::PITCH + col];
-      if (inv) v1 = cswap(v1);
-      if (do_scale) v1 = cscale(v1, scale);
-      *reinterpret_cast<cx2<R>*>(dst) = cx2<R>{v0, v1};
-    } else {
-      *dst = v0;
-    }
-    cl += CSTEP;
-    if (d.split_axis == 1)
-      while (cl >= d.Cl) {
-        cl -= d.Cl;
-        ++pc;
-      }
+  const E* src = ((S - 1) % 2 == 0 ? buf0 : buf1) + mm.row * Cfg::PITCH;
+  E* dst = (S % 2 == 0 ? buf0 : buf1) + mm.row * Cfg::PITCH;
+  if (mm.active)
+    static_stage<Cfg, R, S, SG, DG, ROT>(d, tw, src, dst, gsrc, mm.j, inv, do_scale, scale, mm.peer0, mm.toff);
+  if constexpr (!LAST) {
+    __syncthreads();
+    static_stages<Cfg, R, S + 1>(d, tw, buf0, buf1, gsrc, m, mlast, inv, do_scale, scale);
   }
 }
 
@@ -189,23 +170,39 @@ __global__ void __launch_bounds__((MixedCfg<R, N, T, DOUT>::NT), (MixedCfg<R, N,
   const int o = blockIdx.x / tiles_t;
   const int b = blockIdx.y;
   const int t0 = tt * T;
-  const int row = tid / Cfg::TPR;
-  const int j = tid - row * Cfg::TPR;
-  const bool active = row < T && t0 + row < d.Tn;
   const bool inv = d.inverse != 0;
-  const E* gsrc = (const E*)d.in + ((long long)o * d.is_o + (long long)b * d.is_b + (long long)(t0 + row) * d.is_t);
   const OutBase ob = out_base_for(d, o, b);
-  const int t = t0 + row;
-  const int pt = d.split_axis == 2 ? t / d.Tl : 0;
-  const long long toff = ob.off + (long long)(t - pt * d.Tl) * d.os_t;
   const R scale = (R)d.scale;
   const bool do_scale = d.scale != 1.0;
-  static_stages<Cfg, R, 0>(d, (const E*)d.twiddle, buf0, buf1, gsrc, row, j, active, inv, do_scale, scale, ob.peer + pt,
-                           toff);
-  if constexpr (!DOUT) {
-    // the last stage (index NS-1) wrote buffer (NS-1) % 2
-    static_rot_store<Cfg, R>(d, (Cfg::NS - 1) % 2 == 0 ? buf0 : buf1, o, t0, b, inv, do_scale, scale);
+  // row-wise layout: TPR consecutive threads serve one row
+  MixedThreadMap m;
+  m.row = tid / Cfg::TPR;
+  m.j = tid - m.row * Cfg::TPR;
+  m.active = m.row < T && t0 + m.row < d.Tn;
+  {
+    const int t = t0 + m.row;
+    const int pt = d.split_axis == 2 ? t / d.Tl : 0;
+    m.peer0 = ob.peer + pt;
+    m.toff = ob.off + (long long)(t - pt * d.Tl) * d.os_t;
   }
+  // layout of the last stage of a rotating pass: consecutive threads serve consecutive rows of the same
+  // butterflies, so that the results of one column are stored by neighbouring lanes as one run
+  MixedThreadMap ml = m;
+  if constexpr (!DOUT) {
+    constexpr int RG = T / Cfg::RH;
+    const int r_lo = tid % Cfg::RH;
+    const int bb = (tid / Cfg::RH) % Cfg::CB;
+    const int rest = tid / (Cfg::RH * Cfg::CB);
+    ml.row = r_lo + Cfg::RH * (rest % RG);
+    ml.j = Cfg::CB * (rest / RG) + bb;
+    ml.active = ml.j < Cfg::TPR && t0 + ml.row < d.Tn;
+    const int t = t0 + ml.row;
+    const int pt = d.split_axis == 2 ? t / d.Tl : 0;
+    ml.peer0 = ob.peer + pt;
+    ml.toff = ob.off + (long long)(t - pt * d.Tl) * d.os_t;
+  }
+  const E* gsrc = (const E*)d.in + ((long long)o * d.is_o + (long long)b * d.is_b + (long long)(t0 + m.row) * d.is_t);
+  static_stages<Cfg, R, 0>(d, (const E*)d.twiddle, buf0, buf1, gsrc, m, ml, inv, do_scale, scale);
 }
 
 template <typename R, int N, int T, bool DOUT>
@@ -240,21 +237,15 @@ static int launch_mixed_static_t(const PassDesc& d, cudaStream_t stream) {
 template <typename R, int N>
 static int launch_mixed_static_n(const PassDesc& d, cudaStream_t stream) {
   constexpr int EB = 2 * (int)sizeof(R);
-  if (d.load_t_contig || d.is_c != 1 || d.M != N || d.pitch != mixed_static_pitch(N, EB)) return JD_ERR_UNSUPPORTED;
+  if (d.load_t_contig || d.is_c != 1 || d.M != N) return JD_ERR_UNSUPPORTED;
+  if (d.split_axis == 1 && d.Cl < 2) return JD_ERR_UNSUPPORTED;
   if (!d.store_t_contig) {
     constexpr int T = mixed_static_T(N, EB, false);
-    if (d.os_c != 1 || d.T != T) return JD_ERR_UNSUPPORTED;
+    if (d.os_c != 1 || d.T != T || d.pitch != mixed_static_pitch(N, EB, T)) return JD_ERR_UNSUPPORTED;
     return launch_mixed_static_t<R, N, T, true>(d, stream);
   }
   constexpr int T = mixed_static_T(N, EB, true);
-  if (d.os_t != 1 || d.T != T) return JD_ERR_UNSUPPORTED;
-  if (EB == 8 && T >= 2) {
-    // 16-byte stores of two rows: every address component must be even
-    if ((d.Tl & 1) || (d.Tn & 1) || (d.out_base & 1) || (d.os_c & 1) || (d.os_o & 1) || (d.os_b & 1))
-      return JD_ERR_UNSUPPORTED;
-    for (int p = 0; p < d.npeers; ++p)
-      if ((uintptr_t)d.out[p] % 16) return JD_ERR_UNSUPPORTED;
-  }
+  if (d.os_t != 1 || d.T != T || d.pitch != mixed_static_pitch(N, EB, T)) return JD_ERR_UNSUPPORTED;
   return launch_mixed_static_t<R, N, T, false>(d, stream);
 }
 

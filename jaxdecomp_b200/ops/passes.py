@@ -214,7 +214,8 @@ def choose_tiling(spec: PassSpec, elem_bytes: int, remote: bool) -> dict:
     if spec.fft and not (_is_pow2(C) and C >= 8) and mixed_radix_ok(C, elem_bytes):
         # mixed-radix kernel: two shared-memory buffers of T padded rows
         rowlen = C + 2 * ((C + 15) // 16)
-        pitch = rowlen + (2 - rowlen) % 16 if elem_bytes == 8 else rowlen + (1 - rowlen) % 8
+        lanes = 16 if elem_bytes == 8 else 8  # elements per shared-memory wavefront
+        pitch = rowlen + (lanes // 8 - rowlen) % lanes
         tile_bytes = lambda t: 2 * t * pitch * elem_bytes  # noqa: E731
         T = 1
         while T < 32 and tile_bytes(2 * T) <= 110 * 1024:
@@ -229,6 +230,9 @@ def choose_tiling(spec: PassSpec, elem_bytes: int, remote: bool) -> dict:
             T = max(1, min(_next_pow2(ov), 32))
             while T > 1 and tile_bytes(T) > 220 * 1024:
                 T //= 2
+        # the last stage of a rotating pass reads min(T, 8) rows x lanes / min(T, 8) columns per wavefront:
+        # conflict-free when the pitch equals that column count modulo the wavefront width
+        pitch = rowlen + (lanes // min(T, 8) - rowlen) % lanes
         out.update(fft_mode=3, M=C, T=T, Cc=C, pitch=pitch, logW=_log2(_next_pow2(C)))
         intra_pad = 1
     elif spec.fft:

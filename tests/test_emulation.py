@@ -135,7 +135,7 @@ def test_mixed_radix_selection():
     from jaxdecomp_b200.ops import passes
 
     def mode(n):
-        specs, _ = passes.compile_passes([plan.Fft(2)], (2, 4, n), (1, 1), (0, 0))
+        specs, _ = passes.compile_passes([plan.Fft(2)], (2, 16, n), (1, 1), (0, 0))
         return passes.choose_tiling(specs[0], 8, False)
 
     assert mode(768)["fft_mode"] == 3 and mode(768)["M"] == 768
@@ -146,4 +146,7 @@ def test_mixed_radix_selection():
     t = mode(768)
     assert t["intra_pad"] == 1 and t["pitch"] % 16 == 2 and t["pitch"] >= 768 + 2 * 48
     assert 2 * t["T"] * t["pitch"] * 8 <= 226 * 1024
+    specs, _ = passes.compile_passes([plan.Fft(2)], (2, 4, 768), (1, 1), (0, 0))
+    t4 = passes.choose_tiling(specs[0], 8, False)   # four rows per tile: pitch == 4 (mod 16)
+    assert t4["T"] == 4 and t4["pitch"] % 16 == 4
     assert not passes.mixed_radix_ok(2 * 17, 8)
