@@ -285,6 +285,10 @@ def init_distributed(backend: Optional[str] = None, device: Optional[torch.devic
             device = torch.device("cpu")
     if device.type == "cuda":
         torch.cuda.set_device(device)
+        # keep the rank (and the pinned buffers it allocates from now on) on the GPU's NUMA node
+        from ..utils.affinity import bind_to_device_cpus
+
+        bind_to_device_cpus(device.index if device.index is not None else torch.cuda.current_device())
     if world > 1 and not _dist_ready():
         if backend is None:
             backend = "nccl" if device.type == "cuda" else "gloo"

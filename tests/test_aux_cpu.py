@@ -121,3 +121,26 @@ def test_init_finalize_are_idempotent():
     jd.finalize()
     x = torch.randn(4, 4, 4)
     assert jd.pfft3d(x).shape == (4, 4, 4)
+
+
+def test_cpu_binding_uses_fake_nvml(monkeypatch):
+    """bind_to_device_cpus intersects NVML's device-local CPUs with the allowed set and leaves the mask alone
+    when NVML is missing; tested against a fake NVML and a fake scheduler."""
+    import os
+
+    from jaxdecomp_b200.utils import affinity
+
+    calls = {}
+    monkeypatch.setattr(affinity, "device_local_cpus", lambda idx: {0, 1, 2, 3, 64})
+    monkeypatch.setattr(os, "sched_getaffinity", lambda pid: {1, 2, 5, 6}, raising=False)
+    monkeypatch.setattr(os, "sched_setaffinity", lambda pid, mask: calls.setdefault("mask", set(mask)), raising=False)
+    assert affinity.bind_to_device_cpus(0) == {1, 2}
+    assert calls["mask"] == {1, 2}
+    calls.clear()
+    monkeypatch.setattr(affinity, "device_local_cpus", lambda idx: None)
+    assert affinity.bind_to_device_cpus(0) is None and not calls
+    monkeypatch.setattr(affinity, "device_local_cpus", lambda idx: {1, 2, 5, 6, 9})
+    assert affinity.bind_to_device_cpus(0) is None and not calls   # already inside the local set
+    monkeypatch.setenv("JD_B200_BIND_CPUS", "0")
+    monkeypatch.setattr(affinity, "device_local_cpus", lambda idx: {1})
+    assert affinity.bind_to_device_cpus(0) is None and not calls
