@@ -237,3 +237,53 @@ def _config1_worker(rank, world):
 
 def test_headline_config_on_cpu_ranks():
     run_ranks(_config1_worker, 8)
+
+
+def test_fft_reference_shape_grid_with_large_prime_factors():
+    """The reference's non-power-of-two test shape (29 N, 19 N, 17 N), here with N = 4."""
+    for pdims in ((2, 4), (4, 2)):
+        run_ranks(_fft_worker, 8, pdims, (29 * 4, 19 * 4, 17 * 4), True, torch.complex128)
+
+
+def _spectral_worker(rank, world, pdims):
+    mesh = jd.make_mesh(pdims, ("z", "y"))
+    shape = (16, 8, 32)
+    xg = _global(shape, torch.complex128, seed=3)
+    x = jd.shard(xg, mesh)
+    k = jd.pfft3d(x)
+    k0, k1, k2 = jd.fftfreq3d(k)            # wave numbers of the original axes 0, 1, 2, broadcastable to k.local
+    full = [2 * torch.pi * torch.fft.fftfreq(n, dtype=torch.float64) for n in shape]
+    for axis, kv in enumerate((k0, k1, k2)):
+        dk = jd.ShardedTensor(k.local * (1j * kv), mesh, k.spec)
+        got = jd.pifft3d(dk).gather()
+        view = [1, 1, 1]
+        view[axis] = -1
+        want = torch.fft.ifftn(torch.fft.fftn(xg) * (1j * full[axis].reshape(view)))
+        torch.testing.assert_close(got, want, rtol=1e-10, atol=1e-10)
+
+
+@pytest.mark.parametrize("pdims", [(2, 4), (1, 8)])
+def test_spectral_derivative_with_fftfreq3d(pdims):
+    run_ranks(_spectral_worker, 8, pdims)
+
+
+def _jvp_worker(rank, world):
+    import torch.autograd.forward_ad as fwAD
+
+    mesh = jd.make_mesh((2, 4), ("z", "y"))
+    xg, tg = _global((16, 8, 32), torch.complex128, seed=5), _global((16, 8, 32), torch.complex128, seed=6)
+    x, t = jd.shard(xg, mesh), jd.shard(tg, mesh)
+    with fwAD.dual_level():
+        dual = jd.ShardedTensor(fwAD.make_dual(x.local, t.local), mesh, x.spec)
+        y = jd.pfft3d(dual)
+        primal, tangent = fwAD.unpack_dual(y.local)
+        assert tangent is not None
+        got = jd.ShardedTensor(tangent, mesh, y.spec).gather()
+        torch.testing.assert_close(got, torch.fft.fftn(tg).permute(1, 2, 0), rtol=1e-10, atol=1e-10)
+        z = jd.transposeXtoY(dual)
+        _, tz = fwAD.unpack_dual(z.local)
+        torch.testing.assert_close(tz, jd.transposeXtoY(t).local)
+
+
+def test_forward_mode_derivatives():
+    run_ranks(_jvp_worker, 8)

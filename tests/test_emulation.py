@@ -32,7 +32,8 @@ def _xspec(pdims, names):
 
 @pytest.mark.parametrize("pdims", [(1, 1), (2, 4), (4, 2), (1, 8), (8, 1)])
 @pytest.mark.parametrize("contig", [True, False])
-@pytest.mark.parametrize("dtype,shape", [(torch.complex64, (8, 16, 32)), (torch.complex128, (24, 40, 56))])
+@pytest.mark.parametrize("dtype,shape", [(torch.complex64, (8, 16, 32)), (torch.complex128, (24, 40, 56)),
+                                         (torch.complex128, (29 * 8, 19 * 8, 17 * 8))])
 def test_fft_pipelines(pdims, contig, dtype, shape):
     names = ("a0", "a1")
     x = torch.randn(shape, dtype=dtype, generator=torch.Generator().manual_seed(0))
