@@ -85,7 +85,7 @@ def test_lpt_step_and_gradient_on_gpu():
     lc = lpt_loss(model, nc_)
     ld.backward()
     lc.backward()
-    assert abs(float(ld) - float(lc)) < 1e-3 * abs(float(lc))
+    assert abs(float(ld.detach()) - float(lc.detach())) < 1e-3 * abs(float(lc.detach()))
     g_ref = nc_.local.grad
     err = (nd.local.grad.cpu().double() - g_ref).abs().max() / g_ref.abs().max()
     assert err < 5e-3, float(err)
