@@ -280,7 +280,7 @@ def main():
             "config": {"model": f"pfft3d+pifft3d round trip {n}^3", "global_shape": [n, n, n], "pdims": list(pdims),
                        "parallelism": f"{'slab' if 1 in pdims else 'pencil'} {p0}x{p1}", "backend": backend,
                        "l2": "inputs (>= 1 GiB per GPU) are larger than the 126 MB L2; no flush needed",
-                       "baseline": "published forward-only pfft3d ms of the reference on H100 (BASELINE.md), "
+                       "baseline": "published forward-only pfft3d ms of the reference on H100 (JOSS paper figure), "
                                    "compared as GFLOP/s", "roundtrip_max_rel_err": err},
             "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"], "reasons": clocks["reasons"]},
             "gpu_launches": launches,
