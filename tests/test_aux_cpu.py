@@ -144,3 +144,17 @@ def test_cpu_binding_uses_fake_nvml(monkeypatch):
     monkeypatch.setenv("JD_B200_BIND_CPUS", "0")
     monkeypatch.setattr(affinity, "device_local_cpus", lambda idx: {1})
     assert affinity.bind_to_device_cpus(0) is None and not calls
+
+
+def test_spectral_poisson_example_runs():
+    """The spectral solver example checks itself against the analytic solution."""
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    r = subprocess.run([sys.executable, os.path.join(root, "examples", "spectral_poisson.py"), "--size", "16"],
+                       capture_output=True, text=True, timeout=300, env=env)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert "max abs error" in r.stdout
