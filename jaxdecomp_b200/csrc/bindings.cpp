@@ -14,6 +14,8 @@
 #include <tuple>
 #include <vector>
 
+#include "fft_fast_plan.h"
+#include "fft_mixed.h"
 #include "launch.h"
 #include "runtime.h"
 #include "trace.h"
@@ -108,6 +110,25 @@ PYBIND11_MODULE(_jdb200, m) {
     return py::make_tuple((uintptr_t)t.twiddle, (uintptr_t)t.chirp, (uintptr_t)t.bhat, (uintptr_t)t.tw_stage);
   });
   m.def("clear_fft_tables", &clear_fft_tables);
+  // geometry of the specialised kernels, for consistency tests against the Python tiling rules
+  m.def("mixed_static_geometry", [](int n, int elem_bytes, bool store_t) {
+    py::dict out;
+    const MixedPlan pl = mixed_plan_of(n);
+    const int T = mixed_static_T(n, elem_bytes, store_t);
+    out["T"] = T;
+    out["pitch"] = mixed_static_pitch(n, elem_bytes, T);
+    out["tpr"] = mixed_threads_per_row(pl, T, elem_bytes);
+    py::list rad;
+    for (int s = 0; s < pl.ns; ++s) rad.append(pl.st[s].radix);
+    out["radices"] = rad;
+    return out;
+  });
+  m.def("mixed_last_stage_map", [](int T, int elem_bytes, int tid) {
+    return py::make_tuple(mixed_last_stage_row(T, elem_bytes, tid), mixed_last_stage_j(T, elem_bytes, tid));
+  });
+  m.def("fast_last_stage_map", [](int T, int tid) {
+    return py::make_tuple(fast_last_stage_row(T, tid), fast_last_stage_j(T, tid));
+  });
 
   py::class_<PlanStep>(m, "PlanStep")
       .def(py::init<>())

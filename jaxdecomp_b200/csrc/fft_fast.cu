@@ -144,12 +144,8 @@ __device__ __forceinline__ void apply_tw(const cx<R>* __restrict__ rec, cx<R> (&
 // are stored by neighbouring lanes straight from registers (runs of T elements).
 template <typename Cfg>
 __device__ __forceinline__ void last_stage_map(int tid, int& row, int& j) {
-  const int r_lo = tid % Cfg::RH;
-  const int b = (tid / Cfg::RH) % Cfg::CB;
-  const int rest = tid / 16;
-  constexpr int RG = Cfg::T / Cfg::RH;  // groups of RH rows
-  row = r_lo + Cfg::RH * (rest % RG);
-  j = Cfg::CB * (rest / RG) + b;
+  row = fast_last_stage_row(Cfg::T, tid);
+  j = fast_last_stage_j(Cfg::T, tid);
 }
 
 // One stage on the sixteen values a[k] = row[j + k*M/16] of a thread.

@@ -45,4 +45,16 @@ JD_PLAN_HD constexpr int plan_stage_record0(int logm, int s) {
 JD_PLAN_HD constexpr int plan_stage_records(int logm) { return plan_stage_record0(logm, plan_num_stages(logm)); }
 constexpr int kFastMinLog = 7, kFastMaxLog = 12;
 
+// Thread layout of the last stage of a rotating pass over tiles of T rows (a power of two): sixteen
+// consecutive threads cover RH = min(T, 8) rows x 16/RH butterfly indices, consecutive threads consecutive rows.
+JD_PLAN_HD constexpr int fast_last_stage_row(int T, int tid) {
+  const int rh = T < 8 ? T : 8;
+  return tid % rh + rh * ((tid / 16) % (T / rh));
+}
+JD_PLAN_HD constexpr int fast_last_stage_j(int T, int tid) {
+  const int rh = T < 8 ? T : 8;
+  const int cb = 16 / rh;
+  return cb * ((tid / 16) / (T / rh)) + (tid / rh) % cb;
+}
+
 }  // namespace jdb

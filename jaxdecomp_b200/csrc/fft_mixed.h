@@ -143,6 +143,41 @@ constexpr int mixed_threads_per_row(const MixedPlan& pl, int T, int elem_bytes) 
   return best;
 }
 
+// Geometry rules of the length-specialised kernels (fft_mixed_static.h); ops/passes.py::choose_tiling applies
+// the same ones, and the launcher falls back to the generic kernel when a descriptor was tiled differently.  The tile height follows from the shared-memory
+// budget with the pitch of tall tiles; the final pitch then makes the reads of the last stage of a rotating
+// pass conflict-free: the threads of one shared-memory wavefront (16 lanes of 8-byte elements, 8 lanes of
+// 16-byte ones) cover RH = min(T, 8) rows x CB columns, which needs pitch == CB modulo the wavefront width.
+constexpr int mixed_rowlen(int n) { return n + 2 * ((n + 15) / 16); }
+constexpr int mixed_pitch_mod(int rowlen, int want, int mod) { return rowlen + (((want - rowlen) % mod) + mod) % mod; }
+constexpr int mixed_static_T(int n, int elem_bytes, bool store_t) {
+  const int pitch = elem_bytes == 8 ? mixed_pitch_mod(mixed_rowlen(n), 2, 16) : mixed_pitch_mod(mixed_rowlen(n), 1, 8);
+  int T = 1;
+  while (T < 32 && 2 * (2 * T) * pitch * elem_bytes <= 110 * 1024) T *= 2;
+  if (store_t)
+    while (T * elem_bytes < 64 && 2 * (2 * T) * pitch * elem_bytes <= 220 * 1024) T *= 2;
+  return T;
+}
+constexpr int mixed_static_pitch(int n, int elem_bytes, int T) {
+  const int lanes = elem_bytes == 8 ? 16 : 8;
+  const int rh = T < 8 ? T : 8;
+  return mixed_pitch_mod(mixed_rowlen(n), lanes / rh, lanes);
+}
+
+// Thread layout of the last stage of a rotating pass in the specialised kernels: the threads of one
+// shared-memory wavefront cover RH = min(T, 8) consecutive rows x CB = lanes/RH consecutive butterfly indices.
+constexpr int mixed_last_stage_row(int T, int elem_bytes, int tid) {
+  const int lanes = elem_bytes == 8 ? 16 : 8;
+  const int rh = T < 8 ? T : 8;
+  return tid % rh + rh * ((tid / lanes) % (T / rh));
+}
+constexpr int mixed_last_stage_j(int T, int elem_bytes, int tid) {
+  const int lanes = elem_bytes == 8 ? 16 : 8;
+  const int rh = T < 8 ? T : 8;
+  const int cb = lanes / rh;
+  return cb * ((tid / lanes) / (T / rh)) + (tid / rh) % cb;
+}
+
 JD_HD uint32_t jd_mulhi(uint32_t a, uint32_t b) {
 #if defined(__CUDA_ARCH__)
   return __umulhi(a, b);

@@ -15,27 +15,6 @@
 
 namespace jdb {
 
-// Geometry rules; ops/passes.py::choose_tiling applies the same ones, and the launcher falls back to
-// the generic kernel when a descriptor was tiled differently.  The tile height follows from the shared-memory
-// budget with the pitch of tall tiles; the final pitch then makes the reads of the last stage of a rotating
-// pass conflict-free: the threads of one shared-memory wavefront (16 lanes of 8-byte elements, 8 lanes of
-// 16-byte ones) cover RH = min(T, 8) rows x CB columns, which needs pitch == CB modulo the wavefront width.
-constexpr int mixed_rowlen(int n) { return n + 2 * ((n + 15) / 16); }
-constexpr int mixed_pitch_mod(int rowlen, int want, int mod) { return rowlen + (((want - rowlen) % mod) + mod) % mod; }
-constexpr int mixed_static_T(int n, int elem_bytes, bool store_t) {
-  const int pitch = elem_bytes == 8 ? mixed_pitch_mod(mixed_rowlen(n), 2, 16) : mixed_pitch_mod(mixed_rowlen(n), 1, 8);
-  int T = 1;
-  while (T < 32 && 2 * (2 * T) * pitch * elem_bytes <= 110 * 1024) T *= 2;
-  if (store_t)
-    while (T * elem_bytes < 64 && 2 * (2 * T) * pitch * elem_bytes <= 220 * 1024) T *= 2;
-  return T;
-}
-constexpr int mixed_static_pitch(int n, int elem_bytes, int T) {
-  const int lanes = elem_bytes == 8 ? 16 : 8;
-  const int rh = T < 8 ? T : 8;
-  return mixed_pitch_mod(mixed_rowlen(n), lanes / rh, lanes);
-}
-
 template <typename R, int N_, int T_, bool DOUT_>
 struct MixedCfg {
   static constexpr int N = N_, T = T_;
@@ -52,6 +31,8 @@ struct MixedCfg {
   static constexpr int MINB = SMEM * 2 + 2048 <= 227 * 1024 ? 2 : 1;
   static_assert(NS >= 2 && TPR > 0, "length not supported by the specialised mixed-radix kernel");
   static_assert(SMEM <= 226 * 1024, "tile exceeds shared memory");
+  // the row-major layout of the last rotating stage must reach every (row, butterfly index) pair
+  static_assert(DOUT || CB * ((NT / (RH * CB)) / (T / RH)) >= TPR, "last-stage thread layout does not cover the tile");
 };
 
 // Stage S of the plan on the butterflies of one thread.  SG: inputs come from global memory; DG: outputs go
@@ -189,12 +170,8 @@ __global__ void __launch_bounds__((MixedCfg<R, N, T, DOUT>::NT), (MixedCfg<R, N,
   // butterflies, so that the results of one column are stored by neighbouring lanes as one run
   MixedThreadMap ml = m;
   if constexpr (!DOUT) {
-    constexpr int RG = T / Cfg::RH;
-    const int r_lo = tid % Cfg::RH;
-    const int bb = (tid / Cfg::RH) % Cfg::CB;
-    const int rest = tid / (Cfg::RH * Cfg::CB);
-    ml.row = r_lo + Cfg::RH * (rest % RG);
-    ml.j = Cfg::CB * (rest / RG) + bb;
+    ml.row = mixed_last_stage_row(T, Cfg::EB, tid);
+    ml.j = mixed_last_stage_j(T, Cfg::EB, tid);
     ml.active = ml.j < Cfg::TPR && t0 + ml.row < d.Tn;
     const int t = t0 + ml.row;
     const int pt = d.split_axis == 2 ? t / d.Tl : 0;

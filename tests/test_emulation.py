@@ -151,3 +151,54 @@ def test_mixed_radix_selection():
     t4 = passes.choose_tiling(specs[0], 8, False)   # four rows per tile: pitch == 4 (mod 16)
     assert t4["T"] == 4 and t4["pitch"] % 16 == 4
     assert not passes.mixed_radix_ok(2 * 17, 8)
+
+
+_MIXED_MENU = [96, 192, 384, 768, 1536, 3072, 288, 576, 1152, 2304, 160, 320, 640, 1280, 2560, 200, 400, 800, 1600,
+               250, 500, 1000, 2000, 240, 480, 960, 1920, 448, 896, 1792]
+
+
+@pytest.mark.parametrize("elem_bytes", [8, 16])
+def test_specialised_mixed_kernels_see_the_tiling_they_expect(elem_bytes):
+    """The length-specialised kernels are only used when the planner's tile height and pitch equal the
+    compile-time geometry: both sides must apply the same rules, for plain and for rotating passes."""
+    from jaxdecomp_b200.ops import passes
+
+    nat = native.require()
+    for n in _MIXED_MENU:
+        for steps, store_t in (([plan.Fft(2)], False), ([plan.Fft(2), plan.Perm(plan.ROT_FWD)], True)):
+            specs, _ = passes.compile_passes(steps, (64, 64, n), (1, 1), (0, 0))
+            t = passes.choose_tiling(specs[0], elem_bytes, False)
+            g = nat.mixed_static_geometry(n, elem_bytes, store_t)
+            assert t["fft_mode"] == 3 and (t["T"], t["pitch"]) == (g["T"], g["pitch"]), (n, store_t, t, g)
+            assert g["tpr"] >= 1 and g["T"] * g["tpr"] <= (512 if elem_bytes == 8 else 256)
+            prod = 1
+            for r in g["radices"]:
+                prod *= r
+            assert prod == n and len(g["radices"]) >= 2
+            # two buffers of T rows fit the shared memory of one block
+            assert 2 * g["T"] * g["pitch"] * elem_bytes <= 226 * 1024
+
+
+def test_last_stage_thread_maps_are_bijections():
+    """Rotating passes re-assign threads across rows for the last stage: every (row, butterfly index) pair
+    must be served by exactly one thread, and consecutive threads must hold consecutive rows."""
+    nat = native.require()
+    for T in (2, 4, 8, 16, 32):
+        for upr in (8, 16, 32, 64, 128, 256):
+            nt = T * upr
+            if nt > 1024:
+                continue
+            seen = {nat.fast_last_stage_map(T, tid) for tid in range(nt)}
+            assert seen == {(r, j) for r in range(T) for j in range(upr)}, (T, upr)
+            assert [nat.fast_last_stage_map(T, tid)[0] for tid in range(min(T, 8))] == list(range(min(T, 8)))
+    # the specialised mixed-radix kernels, with the geometry they are compiled for
+    for eb in (8, 16):
+        for n in _MIXED_MENU:
+            g = nat.mixed_static_geometry(n, eb, True)
+            T, tpr = g["T"], g["tpr"]
+            nt = (T * tpr + 31) // 32 * 32
+            got = [nat.mixed_last_stage_map(T, eb, tid) for tid in range(nt)]
+            active = [(r, j) for r, j in got if j < tpr]
+            assert all(0 <= r < T for r, _ in got)
+            assert len(set(active)) == len(active), (eb, n)
+            assert set(active) == {(r, j) for r in range(T) for j in range(tpr)}, (eb, n, T, tpr)
