@@ -32,8 +32,9 @@ def _ops_worker(rank, world):
         p0, p1 = pdims
         for contiguous in (True, False):
             jd.config.update("transpose_axis_contiguous", contiguous)
-            for dtype, shape, tol in ((torch.complex64, (64, 32, 128), 3e-6), (torch.complex128, (24, 40, 56), 1e-12),
-                                      (torch.complex64, (96, 192, 160), 3e-6)):
+            # largest block first: the peer-visible arena then grows once per mesh
+            for dtype, shape, tol in ((torch.complex64, (96, 192, 160), 3e-6), (torch.complex64, (64, 32, 128), 3e-6),
+                                      (torch.complex128, (24, 40, 56), 1e-12)):
                 g = torch.Generator(device="cpu").manual_seed(1234)
                 xg = torch.randn(shape, generator=g, dtype=torch.float64).to(dtype)
                 x = jd.shard(xg.to(dev), mesh)
