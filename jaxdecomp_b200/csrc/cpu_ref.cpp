@@ -39,11 +39,12 @@ template <typename R>
 struct HostStage {
   const MixedStage& st;
   const cx<R>* tw;
+  const cx<R>* tws;
   const cx<R>* src;
   cx<R>* dst;
   template <int RADIX>
   void run() {
-    mixed_stage_row<R, RADIX>(st, tw, src, dst, 0, 1);
+    mixed_stage_row<R, RADIX>(st, tw, tws, src, dst, 0, 1);
   }
 };
 
@@ -54,7 +55,8 @@ static E* mixed_rows_host(const PassDesc& d, const MixedPlan& pl, E* tile, E* ot
     using R = typename elem_traits<E>::real;
     for (int s = 0; s < pl.ns; ++s) {
       for (int r = 0; r < d.T; ++r) {
-        HostStage<R> hs{pl.st[s], (const E*)d.twiddle, tile + (long long)r * d.pitch, other + (long long)r * d.pitch};
+        HostStage<R> hs{pl.st[s], (const E*)d.twiddle, (const E*)d.tw_stage, tile + (long long)r * d.pitch,
+                        other + (long long)r * d.pitch};
         mixed_dispatch(pl.st[s].radix, hs);
       }
       E* tmp = tile;

@@ -245,7 +245,7 @@ __global__ void __launch_bounds__((FastCfg<R, LOGM, LOGT, STORE_T>::NT), (FastCf
     fft_fast_kernel(const __grid_constant__ PassDesc d) {
   using Cfg = FastCfg<R, LOGM, LOGT, STORE_T>;
   using E = cx<R>;
-  constexpr int M = Cfg::M, T = Cfg::T, NT = Cfg::NT, UPR = Cfg::UPR;
+  constexpr int UPR = Cfg::UPR;
   extern __shared__ __align__(16) unsigned char fast_smem[];
   E* sm = reinterpret_cast<E*>(fast_smem);
 

@@ -34,6 +34,7 @@ struct DevStage {
   const PassDesc& d;
   const MixedStage& st;
   const E* tw;
+  const E* tws;   // per-stage twiddle records (or null)
   const E* src;   // shared-memory row (when !SG)
   E* dst;         // shared-memory row (when !DG)
   const E* gsrc;  // global row (when SG)
@@ -59,7 +60,7 @@ struct DevStage {
 #pragma unroll
         for (int q = 0; q < RADIX; ++q) a[q] = src[padidx(bf + q * nb, 1)];
       }
-      const int base = mixed_butterfly<R, RADIX>(st, tw, bf, a);
+      const int base = mixed_butterfly<R, RADIX>(st, tw, tws, bf, a);
       if constexpr (DG) {
 #pragma unroll
         for (int q = 0; q < RADIX; ++q) {
@@ -107,6 +108,7 @@ __global__ void __launch_bounds__(sizeof(R) == 4 ? 512 : 256, 2)
   const int pt = d.split_axis == 2 ? t / d.Tl : 0;
   const long long toff = ob.off + (long long)(t - pt * d.Tl) * d.os_t;
   const E* tw = (const E*)d.twiddle;
+  const E* tws = (const E*)d.tw_stage;
   const R scale = (R)d.scale;
   const bool do_scale = d.scale != 1.0;
 
@@ -120,18 +122,18 @@ __global__ void __launch_bounds__(sizeof(R) == 4 ? 512 : 256, 2)
       const MixedStage& st = pl.st[s];
       if (sg && dg) {
         if constexpr (DIN && DOUT)
-          mixed_dispatch(st.radix, DevStage<R, true, true>{d, st, tw, src, dst, gsrc, j, tpr, inv, do_scale, scale,
+          mixed_dispatch(st.radix, DevStage<R, true, true>{d, st, tw, tws, src, dst, gsrc, j, tpr, inv, do_scale, scale,
                                                            ob.peer + pt, toff});
       } else if (sg) {
         if constexpr (DIN)
-          mixed_dispatch(st.radix, DevStage<R, true, false>{d, st, tw, src, dst, gsrc, j, tpr, inv, do_scale, scale,
+          mixed_dispatch(st.radix, DevStage<R, true, false>{d, st, tw, tws, src, dst, gsrc, j, tpr, inv, do_scale, scale,
                                                             ob.peer + pt, toff});
       } else if (dg) {
         if constexpr (DOUT)
-          mixed_dispatch(st.radix, DevStage<R, false, true>{d, st, tw, src, dst, gsrc, j, tpr, inv, do_scale, scale,
+          mixed_dispatch(st.radix, DevStage<R, false, true>{d, st, tw, tws, src, dst, gsrc, j, tpr, inv, do_scale, scale,
                                                             ob.peer + pt, toff});
       } else {
-        mixed_dispatch(st.radix, DevStage<R, false, false>{d, st, tw, src, dst, gsrc, j, tpr, inv, do_scale, scale,
+        mixed_dispatch(st.radix, DevStage<R, false, false>{d, st, tw, tws, src, dst, gsrc, j, tpr, inv, do_scale, scale,
                                                            ob.peer + pt, toff});
       }
     }

@@ -26,13 +26,14 @@ struct MixedStage {
   int32_t ls_log;    // log2(ls) when ls is a power of two, else -1
   int32_t tw_mul;    // N / (ls * radix): twiddle index of butterfly bf is (bf mod ls) * tw_mul
   uint32_t ls_magic; // floor(2^32 / ls) + 1: bf / ls == mulhi(bf, ls_magic) for bf, ls < 2^16
+  int32_t rec0;      // index of this stage's first twiddle record (stages >= 1; one record per kk < ls)
 };
 
 struct MixedPlan {
   int32_t n;
   int32_t ns;
   int32_t nb_min;    // butterflies per row of the stage with the largest radix
-  int32_t reserved;
+  int32_t nrec;      // twiddle records of all stages: {w, w^2, w^4, w^8} with w = exp(-2 pi i kk tw_mul / n)
   MixedStage st[JD_MIXED_MAX_STAGES];
 };
 
@@ -89,8 +90,10 @@ constexpr MixedPlan mixed_plan_of(int n) {
   }
   pl.n = n;
   pl.ns = ns;
-  int ls = 1, rmax = 1;
+  int ls = 1, rmax = 1, nrec = 0;
   for (int s = 0; s < ns; ++s) {
+    pl.st[s].rec0 = nrec;
+    if (s > 0) nrec += ls;
     pl.st[s].radix = radices[s];
     pl.st[s].nb = n / radices[s];
     pl.st[s].ls = ls;
@@ -103,6 +106,7 @@ constexpr MixedPlan mixed_plan_of(int n) {
     if (radices[s] > rmax) rmax = radices[s];
   }
   pl.nb_min = n / rmax;
+  pl.nrec = nrec;
   return pl;
 }
 
@@ -188,8 +192,9 @@ JD_HD uint32_t jd_mulhi(uint32_t a, uint32_t b) {
 
 // Twiddle + DFT of one butterfly held in a[]; returns the index of output 0
 // (output q goes to that index + q * st.ls).
+// `tws`: the per-stage twiddle records, or null (then the table `tw` of n roots is used).
 template <typename R, int RADIX>
-JD_HD int mixed_butterfly(const MixedStage& st, const cx<R>* tw, int bf, cx<R> (&a)[RADIX]) {
+JD_HD int mixed_butterfly(const MixedStage& st, const cx<R>* tw, const cx<R>* tws, int bf, cx<R> (&a)[RADIX]) {
   int kk = 0, blk = bf;
   if (st.ls > 1) {
     if (st.ls_log >= 0) {
@@ -199,7 +204,10 @@ JD_HD int mixed_butterfly(const MixedStage& st, const cx<R>* tw, int bf, cx<R> (
       blk = (int)jd_mulhi((uint32_t)bf, st.ls_magic);
       kk = bf - blk * st.ls;
     }
-    twiddle_powers<R, RADIX>(tw, kk * st.tw_mul, a);
+    if (tws != nullptr)
+      twiddle_record<R, RADIX>(tws + 4 * (st.rec0 + kk), a);
+    else
+      twiddle_powers<R, RADIX>(tw, kk * st.tw_mul, a);
   }
   dft_any<R, RADIX>(a);
   return blk * st.ls * RADIX + kk;
@@ -207,12 +215,13 @@ JD_HD int mixed_butterfly(const MixedStage& st, const cx<R>* tw, int bf, cx<R> (
 
 // One stage on one row, smem/host buffer to buffer (both in the padded layout of padidx).
 template <typename R, int RADIX>
-JD_HD void mixed_stage_row(const MixedStage& st, const cx<R>* tw, const cx<R>* src, cx<R>* dst, int first, int step) {
+JD_HD void mixed_stage_row(const MixedStage& st, const cx<R>* tw, const cx<R>* tws, const cx<R>* src, cx<R>* dst,
+                           int first, int step) {
   for (int bf = first; bf < st.nb; bf += step) {
     cx<R> a[RADIX];
 #pragma unroll
     for (int q = 0; q < RADIX; ++q) a[q] = src[padidx(bf + q * st.nb, 1)];
-    const int base = mixed_butterfly<R, RADIX>(st, tw, bf, a);
+    const int base = mixed_butterfly<R, RADIX>(st, tw, tws, bf, a);
 #pragma unroll
     for (int q = 0; q < RADIX; ++q) dst[padidx(base + q * st.ls, 1)] = a[q];
   }

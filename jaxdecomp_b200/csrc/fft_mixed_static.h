@@ -39,11 +39,13 @@ struct MixedCfg {
 // to global memory, along the row (ROT false: column c at toff + c) or transposed (ROT true: column c at
 // toff + c * os_c, toff being the position of this thread's row on the destination's fastest axis).
 template <typename Cfg, typename R, int S, bool SG, bool DG, bool ROT>
-__device__ __forceinline__ void static_stage(const PassDesc& d, const cx<R>* __restrict__ tw, const cx<R>* src, cx<R>* dst,
+__device__ __forceinline__ void static_stage(const PassDesc& d, const cx<R>* __restrict__ tw,
+                                             const cx<R>* __restrict__ tws, const cx<R>* src, cx<R>* dst,
                                              const cx<R>* __restrict__ gsrc, int j, bool inv, bool do_scale, R scale,
                                              int peer0, long long toff) {
   using E = cx<R>;
-  constexpr int RADIX = Cfg::PL.st[S].radix, NB = Cfg::PL.st[S].nb, LS = Cfg::PL.st[S].ls, TWM = Cfg::PL.st[S].tw_mul;
+  constexpr int RADIX = Cfg::PL.st[S].radix, NB = Cfg::PL.st[S].nb, LS = Cfg::PL.st[S].ls;
+  constexpr int REC0 = Cfg::PL.st[S].rec0;
   constexpr int TPR = Cfg::TPR;
   constexpr int ITERS = (NB + TPR - 1) / TPR;
 #pragma unroll
@@ -70,7 +72,7 @@ __device__ __forceinline__ void static_stage(const PassDesc& d, const cx<R>* __r
     if constexpr (LS > 1) {
       blk = bf / LS;
       kk = bf - blk * LS;
-      twiddle_powers<R, RADIX>(tw, kk * TWM, a);
+      twiddle_record<R, RADIX>(tws + 4 * (REC0 + kk), a);
     }
     dft_any<R, RADIX>(a);
     const int base = blk * (LS * RADIX) + kk;
@@ -116,7 +118,8 @@ struct MixedThreadMap {
 };
 
 template <typename Cfg, typename R, int S>
-__device__ __forceinline__ void static_stages(const PassDesc& d, const cx<R>* tw, cx<R>* buf0, cx<R>* buf1,
+__device__ __forceinline__ void static_stages(const PassDesc& d, const cx<R>* tw, const cx<R>* tws, cx<R>* buf0,
+                                              cx<R>* buf1,
                                               const cx<R>* gsrc, const MixedThreadMap& m, const MixedThreadMap& mlast,
                                               bool inv, bool do_scale, R scale) {
   using E = cx<R>;
@@ -129,10 +132,10 @@ __device__ __forceinline__ void static_stages(const PassDesc& d, const cx<R>* tw
   const E* src = ((S - 1) % 2 == 0 ? buf0 : buf1) + mm.row * Cfg::PITCH;
   E* dst = (S % 2 == 0 ? buf0 : buf1) + mm.row * Cfg::PITCH;
   if (mm.active)
-    static_stage<Cfg, R, S, SG, DG, ROT>(d, tw, src, dst, gsrc, mm.j, inv, do_scale, scale, mm.peer0, mm.toff);
+    static_stage<Cfg, R, S, SG, DG, ROT>(d, tw, tws, src, dst, gsrc, mm.j, inv, do_scale, scale, mm.peer0, mm.toff);
   if constexpr (!LAST) {
     __syncthreads();
-    static_stages<Cfg, R, S + 1>(d, tw, buf0, buf1, gsrc, m, mlast, inv, do_scale, scale);
+    static_stages<Cfg, R, S + 1>(d, tw, tws, buf0, buf1, gsrc, m, mlast, inv, do_scale, scale);
   }
 }
 
@@ -179,7 +182,7 @@ __global__ void __launch_bounds__((MixedCfg<R, N, T, DOUT>::NT), (MixedCfg<R, N,
     ml.toff = ob.off + (long long)(t - pt * d.Tl) * d.os_t;
   }
   const E* gsrc = (const E*)d.in + ((long long)o * d.is_o + (long long)b * d.is_b + (long long)(t0 + m.row) * d.is_t);
-  static_stages<Cfg, R, 0>(d, (const E*)d.twiddle, buf0, buf1, gsrc, m, ml, inv, do_scale, scale);
+  static_stages<Cfg, R, 0>(d, (const E*)d.twiddle, (const E*)d.tw_stage, buf0, buf1, gsrc, m, ml, inv, do_scale, scale);
 }
 
 template <typename R, int N, int T, bool DOUT>
@@ -214,7 +217,7 @@ static int launch_mixed_static_t(const PassDesc& d, cudaStream_t stream) {
 template <typename R, int N>
 static int launch_mixed_static_n(const PassDesc& d, cudaStream_t stream) {
   constexpr int EB = 2 * (int)sizeof(R);
-  if (d.load_t_contig || d.is_c != 1 || d.M != N) return JD_ERR_UNSUPPORTED;
+  if (d.load_t_contig || d.is_c != 1 || d.M != N || d.tw_stage == nullptr) return JD_ERR_UNSUPPORTED;
   if (d.split_axis == 1 && d.Cl < 2) return JD_ERR_UNSUPPORTED;
   if (!d.store_t_contig) {
     constexpr int T = mixed_static_T(N, EB, false);

@@ -220,16 +220,15 @@ JD_HD cx<R> tw_load(const cx<R>* p) {
 #endif
 }
 
-// a[q] *= w^q for q = 1..RADIX-1 with w = tw[ti].  The powers w^2, w^4, w^8 are
-// read from the table (the caller guarantees (RADIX-1)*ti < table length); the
-// others are products of those.
+// a[q] *= w^q for q = 1..RADIX-1 given w, w^2, w^4 and w^8 (only those below RADIX are used); the
+// other powers are products of them.
 template <typename R, int RADIX>
-JD_HD void twiddle_powers(const cx<R>* tw, int ti, cx<R> (&a)[RADIX]) {
+JD_HD void twiddle_apply(cx<R> w1, cx<R> w2, cx<R> w4, cx<R> w8, cx<R> (&a)[RADIX]) {
   cx<R> w[RADIX < 8 ? RADIX : 8];
-  w[1] = tw_load(tw + ti);
+  w[1] = w1;
   a[1] = cmul(a[1], w[1]);
   if constexpr (RADIX > 2) {
-    w[2] = tw_load(tw + 2 * ti);
+    w[2] = w2;
     a[2] = cmul(a[2], w[2]);
   }
   if constexpr (RADIX > 3) {
@@ -237,7 +236,7 @@ JD_HD void twiddle_powers(const cx<R>* tw, int ti, cx<R> (&a)[RADIX]) {
     a[3] = cmul(a[3], w[3]);
   }
   if constexpr (RADIX > 4) {
-    w[4] = tw_load(tw + 4 * ti);
+    w[4] = w4;
     a[4] = cmul(a[4], w[4]);
   }
   if constexpr (RADIX > 5) {
@@ -253,11 +252,56 @@ JD_HD void twiddle_powers(const cx<R>* tw, int ti, cx<R> (&a)[RADIX]) {
     a[7] = cmul(a[7], w[7]);
   }
   if constexpr (RADIX > 8) {
-    const cx<R> w8 = tw_load(tw + 8 * ti);
     a[8] = cmul(a[8], w8);
 #pragma unroll
     for (int q = 9; q < RADIX; ++q) a[q] = cmul(a[q], cmul(w[q - 8], w8));
   }
+}
+
+// Twiddles from the table of N roots: w = tw[ti]; w^2, w^4, w^8 are read from the table as well (the
+// caller guarantees (RADIX-1)*ti < table length).
+template <typename R, int RADIX>
+JD_HD void twiddle_powers(const cx<R>* tw, int ti, cx<R> (&a)[RADIX]) {
+  const cx<R> w1 = tw_load(tw + ti);
+  cx<R> w2 = w1, w4 = w1, w8 = w1;
+  if constexpr (RADIX > 2) w2 = tw_load(tw + 2 * ti);
+  if constexpr (RADIX > 4) w4 = tw_load(tw + 4 * ti);
+  if constexpr (RADIX > 8) w8 = tw_load(tw + 8 * ti);
+  twiddle_apply<R, RADIX>(w1, w2, w4, w8, a);
+}
+
+// Twiddles from a per-stage record {w, w^2, w^4, w^8} (32 bytes for complex64, read as two 16-byte words):
+// the records of consecutive butterflies are contiguous, so a warp's reads coalesce.
+template <typename R, int RADIX>
+JD_HD void twiddle_record(const cx<R>* rec, cx<R> (&a)[RADIX]) {
+  cx<R> w1, w2, w4, w8;
+#if defined(__CUDA_ARCH__)
+  if constexpr (sizeof(R) == 4) {
+    const float4 lo = __ldg(reinterpret_cast<const float4*>(rec));
+    w1 = cx<R>{lo.x, lo.y};
+    w2 = cx<R>{lo.z, lo.w};
+    w4 = w1;
+    w8 = w1;
+    if constexpr (RADIX > 4) {
+      const float4 hi = __ldg(reinterpret_cast<const float4*>(rec) + 1);
+      w4 = cx<R>{hi.x, hi.y};
+      w8 = cx<R>{hi.z, hi.w};
+    }
+  } else {
+    w1 = tw_load(rec);
+    w2 = tw_load(rec + 1);
+    w4 = w1;
+    w8 = w1;
+    if constexpr (RADIX > 4) w4 = tw_load(rec + 2);
+    if constexpr (RADIX > 8) w8 = tw_load(rec + 3);
+  }
+#else
+  w1 = rec[0];
+  w2 = rec[1];
+  w4 = rec[2];
+  w8 = rec[3];
+#endif
+  twiddle_apply<R, RADIX>(w1, w2, w4, w8, a);
 }
 
 }  // namespace jdb

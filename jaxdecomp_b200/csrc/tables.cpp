@@ -19,6 +19,7 @@
 #include <vector>
 
 #include "fft_fast_plan.h"
+#include "fft_mixed.h"
 #include "runtime.h"
 
 namespace jdb {
@@ -120,6 +121,20 @@ FftTables get_fft_tables(int C, int M, int elem_bytes, bool device) {
           }
       }
       ts.tw_stage = upload(rec, elem_bytes, device);
+    } else if (C == M) {
+      // mixed-radix plan: records {w, w^2, w^4, w^8} per stage >= 1 and kk < ls, w = exp(-2 pi i kk tw_mul / M)
+      const MixedPlan pl = mixed_plan_of(M);
+      if (pl.ns > 0 && pl.nrec > 0) {
+        std::vector<cld> rec((size_t)pl.nrec * 4);
+        for (int s = 1; s < pl.ns; ++s)
+          for (int kk = 0; kk < pl.st[s].ls; ++kk)
+            for (int p = 0; p < 4; ++p) {
+              const long long e = ((long long)kk * pl.st[s].tw_mul * (1LL << p)) % M;
+              const long double ang = -2.0L * kPi * (long double)e / (long double)M;
+              rec[((size_t)pl.st[s].rec0 + kk) * 4 + p] = cld(cosl(ang), sinl(ang));
+            }
+        ts.tw_stage = upload(rec, elem_bytes, device);
+      }
     }
     if (C != M) {
       if (M < 2 * C - 1) throw std::runtime_error("tables: Bluestein length too short");
