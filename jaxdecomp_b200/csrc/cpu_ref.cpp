@@ -149,6 +149,7 @@ int validate_pass(const PassDesc& d) {
     return JD_ERR_INVALID_ARG;
   }
   if (d.elem_bytes != 4 && d.elem_bytes != 8 && d.elem_bytes != 16) return JD_ERR_INVALID_ARG;
+  if (d.mul_mode != 0 || d.mul != nullptr) return JD_ERR_INVALID_ARG;  // reserved fields
   if (d.load_t_contig ? d.is_t != 1 : d.is_c != 1) return JD_ERR_INVALID_ARG;
   if (d.store_t_contig ? d.os_t != 1 : d.os_c != 1) return JD_ERR_INVALID_ARG;
   if (d.fft_mode == JD_COPY) {

@@ -57,7 +57,8 @@ struct PassDesc {
   int32_t load_t_contig;  // 1: input is contiguous along t (is_t == 1), else along c
   int32_t store_t_contig; // 1: output is contiguous along t (os_t == 1), else along c
   int32_t use_bulk;       // 1: fetch rows with bulk async copies (needs 16-byte aligned rows)
-  int32_t mul_mode;       // 0 none; 1 multiply the result by mul[] (same indexing as the output of peer 0)
+  int32_t mul_mode;       // reserved for a fused pointwise multiplier in the store; must be 0 (descriptors with
+                          // another value are rejected by validate_pass)
   int32_t vec_in;         // 1: 8-byte elements may be loaded two at a time (16-byte accesses)
   int32_t vec_out;        // 1: 8-byte elements may be stored two at a time
   int32_t intra_pad;      // 1: rows carry two unused slots after every 16 columns (bank-conflict-free FFT exchanges)
@@ -71,7 +72,7 @@ struct PassDesc {
   const void* tw_stage;   // per-stage twiddle records of the specialised power-of-two kernel (fft_fast_plan.h), or null
   const void* chirp;      // Bluestein: C entries exp(-i*pi*n^2/C)
   const void* bhat;       // Bluestein: M entries FFT_M(conj chirp, wrapped) / M
-  const void* mul;        // optional pointwise multiplier
+  const void* mul;        // reserved (see mul_mode); must be null
 };
 
 // (c, t, o, b) of the local block -> destination peer and element offset there.
