@@ -202,3 +202,68 @@ def test_last_stage_thread_maps_are_bijections():
             assert all(0 <= r < T for r, _ in got)
             assert len(set(active)) == len(active), (eb, n)
             assert set(active) == {(r, j) for r in range(T) for j in range(tpr)}, (eb, n, T, tpr)
+
+
+def _host_table(ptr, count, dtype):
+    import ctypes
+
+    import numpy as np
+
+    nbytes = count * np.dtype(dtype).itemsize
+    buf = (ctypes.c_char * nbytes).from_address(ptr)
+    return np.frombuffer(buf, dtype=dtype, count=count).copy()
+
+
+@pytest.mark.parametrize("elem_bytes", [8, 16])
+def test_stage_twiddle_records_of_the_power_of_two_kernel(elem_bytes):
+    """The specialised power-of-two kernel has no CPU path, so its per-stage twiddle records are checked
+    here: record kk of stage s holds w, w^2, w^4, w^8 with w = exp(-2 pi i kk / (Ls * radix))."""
+    import numpy as np
+
+    nat = native.require()
+    radix_log = {7: [4, 3], 8: [4, 4], 9: [3, 3, 3], 10: [4, 3, 3], 11: [4, 4, 3], 12: [4, 4, 4]}
+    cdt = np.complex64 if elem_bytes == 8 else np.complex128
+    for logm, plan_ in radix_log.items():
+        m = 1 << logm
+        tw, _, _, tws = nat.get_fft_tables(m, m, elem_bytes, False)
+        assert tw and tws
+        roots = _host_table(tw, m, cdt)
+        np.testing.assert_allclose(roots, np.exp(-2j * np.pi * np.arange(m) / m), atol=1e-7 if elem_bytes == 8 else 1e-15)
+        ls, rec0 = 1, 0
+        nrec = sum((1 << sum(plan_[:s])) for s in range(1, len(plan_)))
+        recs = _host_table(tws, nrec * 4, cdt).reshape(nrec, 4)
+        for s, rl in enumerate(plan_):
+            if s > 0:
+                span = ls << rl
+                kk = np.arange(ls)[:, None]
+                want = np.exp(-2j * np.pi * (kk << np.arange(4)[None, :]) / span)
+                np.testing.assert_allclose(recs[rec0:rec0 + ls], want, atol=1e-7 if elem_bytes == 8 else 1e-15)
+                rec0 += ls
+            ls <<= rl
+
+
+def test_stage_twiddle_records_of_the_mixed_radix_kernels():
+    import numpy as np
+
+    nat = native.require()
+    for n in (768, 1000, 96, 2310):
+        g = nat.mixed_static_geometry(n, 16, False)
+        tw, _, _, tws = nat.get_fft_tables(n, n, 16, False)
+        assert tw and tws
+        ls, rec0 = 1, 0
+        radices = list(g["radices"])
+        nrec = 0
+        acc = 1
+        for s, r in enumerate(radices):
+            if s > 0:
+                nrec += acc
+            acc *= r
+        recs = _host_table(tws, nrec * 4, np.complex128).reshape(nrec, 4)
+        for s, r in enumerate(radices):
+            if s > 0:
+                tw_mul = n // (ls * r)
+                kk = np.arange(ls)[:, None]
+                want = np.exp(-2j * np.pi * ((kk * tw_mul * (1 << np.arange(4))[None, :]) % n) / n)
+                np.testing.assert_allclose(recs[rec0:rec0 + ls], want, atol=1e-15)
+                rec0 += ls
+            ls *= r
