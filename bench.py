@@ -11,9 +11,12 @@ reference's benchmark alternates on one buffer (benchmarks/bench.py:68-70).
 Timing: CUDA events on the launching stream between barrier+synchronize pairs,
 maximum over ranks.  Rank 0 prints one JSON line.
 
-`--impl reference` would run the unmodified reference (JAX) from
-baseline/_ref; JAX is not installable offline on this image, so that arm
-reports itself unavailable.
+`--impl reference` runs the unmodified reference (jaxdecomp on JAX) from
+baseline/_ref through its own API (benchmarks/reference_arm.py) and reports
+itself unavailable when it cannot be imported.  `--impl torch` is the same
+algorithm on library kernels (cuFFT + NCCL all-to-all + permute copies), the
+same-machine baseline; the `ours` arm also times three steps of it and reports
+them as config.same_box_torch_ms.
 """
 from __future__ import annotations
 
@@ -35,19 +38,11 @@ PUBLISHED_FWD_MS = {2: 29.0, 4: 13.0, 8: 16.0}
 
 
 def reference_arm(args):
-    reason = None
-    try:
-        sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
-        import jax  # noqa: F401
-        import jaxdecomp  # noqa: F401
-    except Exception as e:  # noqa: BLE001
-        reason = (f"reference not installable offline: jax/jaxlib and nanobind are absent from the image and the wheelhouse "
-                  f"({type(e).__name__}: {e})")
-    if reason is None:
-        reason = "reference import succeeded unexpectedly but no runner is wired for it on this image"
-    if int(os.environ.get("RANK", "0")) == 0:
-        print(json.dumps({"impl": "reference", "unavailable": reason}))
-    return 0
+    """Run the unmodified reference from baseline/_ref through its own API (benchmarks/reference_arm.py);
+    prints the `unavailable` line when jax or jaxdecomp cannot be imported."""
+    from benchmarks import reference_arm as ref
+
+    return ref.run(args, ROOT, PUBLISHED_FWD_MS)
 
 
 class ClockSampler(threading.Thread):
@@ -134,6 +129,15 @@ def pick_pdims(n: int, override: str | None):
     return (1, n)
 
 
+def _rel_err(a, b, world, dist, torch):
+    num = (a - b).abs().max()
+    den = b.abs().max()
+    t = torch.stack([num, den]).to(torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t[0] / t[1].clamp_min(1e-30))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -143,7 +147,13 @@ def main():
     ap.add_argument("--size", type=int, default=1024, help="grid points per side (headline: 1024)")
     ap.add_argument("--dtype", default="c64", choices=["c64", "c128"])
     ap.add_argument("--pdims", default=None, help="process grid as P0xP1 (default: slab 1xN)")
+    ap.add_argument("--transport", default=None, choices=["p2p", "p2p_pl"],
+                    help="native transpose transport: plain or pipelined (default: the library's default)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the forward check against the baseline backend, the same-machine baseline timing "
+                         "and the pencil timing")
+    ap.add_argument("--ref-backend", default="jax", help="backend string passed to the reference (reference arm only)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -160,35 +170,72 @@ def main():
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run for N > 1")
     device = jd.init_distributed()
     backend = "b200" if args.impl == "ours" else "torch"
+    if args.transport:
+        jd.config.update("transpose_comm_backend",
+                         jd.TRANSPOSE_COMM_P2P_PL if args.transport == "p2p_pl" else jd.TRANSPOSE_COMM_P2P)
     warmup = max(3, args.warmup)
     steps = max(1, args.steps)
     n = args.size
     dtype = torch.complex64 if args.dtype == "c64" else torch.complex128
-    pdims = pick_pdims(world, args.pdims)
-    mesh = jd.make_mesh(pdims, ("z", "y"))
-    p0, p1 = pdims
-    lshape = (n // p0, n // p1, n)
-    gen = torch.Generator(device=device).manual_seed(0 + rank)
     real_dtype = torch.float32 if dtype == torch.complex64 else torch.float64
-    x0 = torch.complex(torch.randn(lshape, generator=gen, device=device, dtype=real_dtype),
-                       torch.randn(lshape, generator=gen, device=device, dtype=real_dtype))
-    x = jd.ShardedTensor(x0, mesh)
+    pdims = pick_pdims(world, args.pdims)
+    p0, p1 = pdims
+    esize = 8 if dtype == torch.complex64 else 16
+    # one workspace for everything this run does: no arena growth inside or between the timed loops
+    jd.init(workspace_bytes=(n ** 3 // world) * esize)
 
     def sync_all():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
+    def make_input(mesh_pdims, size):
+        q0, q1 = mesh_pdims
+        shape = (size // q0, size // q1, size)
+        gen = torch.Generator(device=device).manual_seed(0 + rank)
+        return torch.complex(torch.randn(shape, generator=gen, device=device, dtype=real_dtype),
+                             torch.randn(shape, generator=gen, device=device, dtype=real_dtype))
+
+    def timed_loop(mesh, x0, be, k, w):
+        """w warm-up and k timed round trips; CUDA events on the launching stream, max over ranks."""
+        x = jd.ShardedTensor(x0, mesh)
+        v = x
+        for _ in range(w):
+            v = jd.pifft3d(jd.pfft3d(v, backend=be), backend=be)
+        sync_all()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        for _ in range(k):
+            v = jd.pifft3d(jd.pfft3d(v, backend=be), backend=be)
+        ev1.record()
+        sync_all()
+        t = torch.tensor([ev0.elapsed_time(ev1) / k], device=device, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    mesh = jd.make_mesh(pdims, ("z", "y"))
+    lshape = (n // p0, n // p1, n)
+    extras = {}
+    # ---- forward result against the baseline backend (cuFFT + all-to-all) on the run's own mesh, 256^3 ----
+    if backend == "b200" and not args.no_extras:
+        small = min(256, n)
+        xs = jd.ShardedTensor(make_input(pdims, small), mesh)
+        ks = jd.pfft3d(xs, backend="b200")
+        kr = jd.pfft3d(xs, backend="torch")
+        extras["forward_max_rel_err_vs_torch"] = _rel_err(ks.local, kr.local, world, dist, torch)
+        extras["forward_check_shape"] = [small] * 3
+        del xs, ks, kr
+
+    x0 = make_input(pdims, n)
+    x = jd.ShardedTensor(x0, mesh)
+
     def step(v):
         return jd.pifft3d(jd.pfft3d(v, backend=backend), backend=backend)
 
     # correctness of the timed path (also the first warm-up): round trip returns the input
     y = step(x)
-    err = float(((y.local - x0).abs().max() / x0.abs().max()).item())
-    if world > 1:
-        t = torch.tensor([err], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        err = float(t.item())
+    err = _rel_err(y.local, x0, world, dist, torch)
     v = x
     for _ in range(warmup):
         v = step(v)
@@ -196,6 +243,7 @@ def main():
     sampler = ClockSampler(device.index or 0)
     sampler.start()
     launches0 = b200_backend.launches(mesh) if backend == "b200" else 0
+    sections0 = b200_backend.get_runtime(mesh).rt.pipelined_sections() if backend == "b200" else 0
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sync_all()
     ev0.record()
@@ -212,29 +260,49 @@ def main():
     ms = float(t.item())
     if backend == "b200":
         b200_backend.check_status(mesh, sync=True)
+        extras["pipelined_sections_per_step"] = \
+            (b200_backend.get_runtime(mesh).rt.pipelined_sections() - sections0) / steps
+        extras["transport"] = jd.config.transpose_comm_backend.name
+    del v, y
 
-    # ---- end-to-end: per step, H2D of the step's input from pinned memory and D2H of a result scalar ----
+    # ---- same-machine baseline (library kernels) and the pencil decomposition, a few steps each ----
+    if backend == "b200" and not args.no_extras:
+        extras["same_box_torch_ms"] = timed_loop(mesh, x0, "torch", 3, 1)
+        if world >= 4:
+            pp = (2, world // 2)
+            pmesh = jd.make_mesh(pp, ("z", "y"))
+            xp = make_input(pp, n)
+            extras[f"pencil_{pp[0]}x{pp[1]}_ms"] = timed_loop(pmesh, xp, "b200", max(3, steps // 2), 3)
+            b200_backend.check_status(pmesh, sync=True)
+            del xp
+        torch.cuda.empty_cache()
+
+    # ---- end to end: per step, the input comes from pinned host memory and the result goes back to it ----
     e2e = None
     if not args.no_e2e:
-        del v, y
-        host = torch.empty(lshape, dtype=dtype, pin_memory=True)
-        host.copy_(x0)
+        host_in = torch.empty(lshape, dtype=dtype, pin_memory=True)
+        host_in.copy_(x0)
+        host_out = [torch.empty(lshape, dtype=dtype, pin_memory=True) for _ in range(2)]
         bufs = [torch.empty_like(x0), x0]
-        copy_stream = torch.cuda.Stream()
+        h2d, d2h = torch.cuda.Stream(), torch.cuda.Stream()
         main_stream = torch.cuda.current_stream()
         ready = [torch.cuda.Event(), torch.cuda.Event()]
         consumed = [torch.cuda.Event(), torch.cuda.Event()]
+        done = [torch.cuda.Event(), torch.cuda.Event()]
+        copied = [torch.cuda.Event(), torch.cuda.Event()]
 
         def prefetch(i):
-            with torch.cuda.stream(copy_stream):
-                copy_stream.wait_event(consumed[i])
-                bufs[i].copy_(host, non_blocking=True)
-                ready[i].record(copy_stream)
+            with torch.cuda.stream(h2d):
+                h2d.wait_event(consumed[i])
+                bufs[i].copy_(host_in, non_blocking=True)
+                ready[i].record(h2d)
 
         def e2e_steps(k):
-            consumed[0].record(main_stream)
-            consumed[1].record(main_stream)
+            for i in (0, 1):
+                consumed[i].record(main_stream)
+                copied[i].record(d2h)
             prefetch(0)
+            outs = [None, None]
             acc = 0.0
             for s in range(k):
                 i = s % 2
@@ -243,7 +311,18 @@ def main():
                 main_stream.wait_event(ready[i])
                 out = step(jd.ShardedTensor(bufs[i], mesh))
                 consumed[i].record(main_stream)
-                acc += float(out.local.real[0, 0, :8].sum().item())  # device -> host read of a result scalar
+                done[i].record(main_stream)
+                outs[i] = out.local
+                with torch.cuda.stream(d2h):
+                    d2h.wait_event(done[i])
+                    host_out[i].copy_(outs[i], non_blocking=True)  # the result field goes back to the host
+                    copied[i].record(d2h)
+                outs[i].record_stream(d2h)
+                if s >= 1:  # read a value of the previous step's result on the host once its copy has landed
+                    copied[1 - i].synchronize()
+                    acc += float(host_out[1 - i][0, 0, 0].real)
+            copied[(k - 1) % 2].synchronize()
+            acc += float(host_out[(k - 1) % 2][0, 0, 0].real)
             return acc
 
         e2e_steps(2)
@@ -252,6 +331,8 @@ def main():
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         e2e_steps(steps)
+        d2h.synchronize()
+        main_stream.wait_stream(d2h)
         e1.record()
         sync_all()
         e_ms = e0.elapsed_time(e1) / steps
@@ -259,8 +340,9 @@ def main():
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e_ms = float(t.item())
+        nbytes = host_in.numel() * host_in.element_size() * world
         e2e = {"ms_per_step": e_ms, "wall_ms_per_step": (time.perf_counter() - t0) * 1e3 / steps,
-               "h2d_bytes_per_step": host.numel() * host.element_size() * world, "d2h_bytes_per_step": 4 * world}
+               "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes}
 
     total = float(n) ** 3
     flops = 2 * 5.0 * total * math.log2(total)  # forward + inverse, 5 N log2 N each
@@ -268,6 +350,13 @@ def main():
     base = PUBLISHED_FWD_MS.get(world) if (n == 1024 and dtype == torch.complex64) else None
     base_gflops = (5.0 * total * math.log2(total) / (base * 1e-3) / 1e9) if base else None
     if rank == 0:
+        cfg = {"model": f"pfft3d+pifft3d round trip {n}^3", "global_shape": [n, n, n], "pdims": list(pdims),
+               "parallelism": f"{'slab' if 1 in pdims else 'pencil'} {p0}x{p1}", "backend": backend,
+               "l2": "inputs (>= 1 GiB per GPU) are larger than the 126 MB L2; no flush needed",
+               "baseline": "context only: published forward-only pfft3d ms of the reference on H100 (JOSS paper "
+                           "figure, other hardware), compared as GFLOP/s",
+               "roundtrip_max_rel_err": err}
+        cfg.update(extras)
         line = {
             "metric": "pfft3d+pifft3d GFLOP/s (5*N*log2(N) per transform), 1024^3 complex64" if n == 1024 else
                       f"pfft3d+pifft3d GFLOP/s, {n}^3",
@@ -277,11 +366,7 @@ def main():
             "dtype": "complex64 (fp32)" if dtype == torch.complex64 else "complex128 (fp64)",
             "data": "synthetic: N(0,1) real and imaginary parts, seeded per rank",
             "impl": args.impl,
-            "config": {"model": f"pfft3d+pifft3d round trip {n}^3", "global_shape": [n, n, n], "pdims": list(pdims),
-                       "parallelism": f"{'slab' if 1 in pdims else 'pencil'} {p0}x{p1}", "backend": backend,
-                       "l2": "inputs (>= 1 GiB per GPU) are larger than the 126 MB L2; no flush needed",
-                       "baseline": "published forward-only pfft3d ms of the reference on H100 (JOSS paper figure), "
-                                   "compared as GFLOP/s", "roundtrip_max_rel_err": err},
+            "config": cfg,
             "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"], "reasons": clocks["reasons"]},
             "gpu_launches": launches,
         }
@@ -290,8 +375,9 @@ def main():
                            "ms_per_step": e2e["ms_per_step"],
                            "h2d_bytes_per_step": e2e["h2d_bytes_per_step"],
                            "d2h_bytes_per_step": e2e["d2h_bytes_per_step"],
-                           "note": "input copied from pinned host memory every step (double-buffered on a copy "
-                                   "stream), one result scalar read back per step; bytes are totals over all ranks"}
+                           "note": "every step copies its input from pinned host memory and its result field back to "
+                                   "pinned host memory (separate copy streams, double-buffered), and the host reads a "
+                                   "value of each result; bytes are totals over all ranks"}
         print(json.dumps(line))
     if world > 1:
         dist.barrier()

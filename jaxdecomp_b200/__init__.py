@@ -51,6 +51,7 @@ from .utils.api import (
     get_transpose_workspace_size,
     init,
     make_config,
+    reserve_workspace,
 )
 from .utils.checkpoint import load_sharded, save_sharded
 from .utils.config import (
@@ -72,6 +73,7 @@ from .utils.config import (
     TRANSPOSE_COMM_NVSHMEM,
     TRANSPOSE_COMM_NVSHMEM_PL,
     TRANSPOSE_COMM_P2P,
+    TRANSPOSE_COMM_P2P_PL,
     TRANSPOSE_XY,
     TRANSPOSE_XZ,
     TRANSPOSE_YX,
@@ -89,7 +91,7 @@ __version__ = "0.1.0"
 
 __all__ = [
     "config", "init", "finalize", "get_pencil_info", "get_autotuned_config", "make_config", "autotune",
-    "get_fft_workspace_size", "get_transpose_workspace_size", "get_halo_workspace_size",
+    "get_fft_workspace_size", "get_transpose_workspace_size", "get_halo_workspace_size", "reserve_workspace",
     "halo_exchange", "halo_exchange_", "halo_accumulate", "halo_reduce", "pad_halo", "unpad_halo",
     "pfft3d", "pifft3d", "fftfreq3d", "rfftfreq3d",
     "transposeXtoY", "transposeYtoX", "transposeYtoZ", "transposeZtoY", "transposeXtoZ", "transposeZtoX",
@@ -100,7 +102,7 @@ __all__ = [
     "HALO_COMM_MPI", "HALO_COMM_MPI_BLOCKING", "HALO_COMM_NCCL", "HALO_COMM_NVSHMEM", "HALO_COMM_NVSHMEM_BLOCKING",
     "HALO_COMM_P2P",
     "TRANSPOSE_COMM_MPI_A2A", "TRANSPOSE_COMM_MPI_P2P", "TRANSPOSE_COMM_MPI_P2P_PL", "TRANSPOSE_COMM_NCCL",
-    "TRANSPOSE_COMM_NCCL_PL", "TRANSPOSE_COMM_NVSHMEM", "TRANSPOSE_COMM_NVSHMEM_PL", "TRANSPOSE_COMM_P2P",
+    "TRANSPOSE_COMM_NCCL_PL", "TRANSPOSE_COMM_NVSHMEM", "TRANSPOSE_COMM_NVSHMEM_PL", "TRANSPOSE_COMM_P2P", "TRANSPOSE_COMM_P2P_PL",
     "HaloCommBackend", "TransposeCommBackend", "TransposeType", "Decomposition",
     "Mesh", "make_mesh", "set_mesh", "current_mesh", "single_rank_mesh", "init_distributed",
     "ShardedTensor", "shard", "PartitionSpec", "P", "NamedSharding", "PencilInfo", "GridConfig",

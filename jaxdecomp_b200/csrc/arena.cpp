@@ -42,6 +42,7 @@ SymmetricArena::SymmetricArena(size_t bytes, int world, int me) : bytes_(bytes),
 }
 
 std::string SymmetricArena::export_handles() const {
+  exported_ = true;
   cudaIpcMemHandle_t h[2];
   check(cudaIpcGetMemHandle(&h[0], data_[me_]), "cudaIpcGetMemHandle(data)");
   check(cudaIpcGetMemHandle(&h[1], flags_[me_]), "cudaIpcGetMemHandle(flags)");
@@ -75,17 +76,22 @@ void SymmetricArena::close_peers() {
   cudaGetLastError();
 }
 
-void SymmetricArena::close() {
+void SymmetricArena::close(bool free_own) {
   if (closed_) return;
   closed_ = true;
   close_peers();
-  if (data_[me_]) cudaFree(data_[me_]);
-  if (flags_[me_]) cudaFree(flags_[me_]);
+  // Peers may still have this rank's blocks mapped (and be storing into them or polling the flags)
+  // unless the ranks synchronised on the host after phase 1.  Freeing exported memory that an importer
+  // still uses is undefined, so without that guarantee the blocks are left to process tear-down.
+  if (free_own || world_ == 1 || !exported_) {
+    if (data_[me_]) cudaFree(data_[me_]);
+    if (flags_[me_]) cudaFree(flags_[me_]);
+  }
   data_[me_] = flags_[me_] = nullptr;
   cudaGetLastError();
 }
 
-SymmetricArena::~SymmetricArena() { close(); }
+SymmetricArena::~SymmetricArena() { close(false); }
 
 HostStatus::HostStatus() {
   void* h = nullptr;

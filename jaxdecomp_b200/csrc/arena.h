@@ -20,7 +20,10 @@ class SymmetricArena {
   std::string export_handles() const;                         // opaque blob to all-gather
   void open_peers(const std::vector<std::string>& handles);  // blobs of all ranks, indexed by rank
   void close_peers();  // phase 1 of tear-down: unmap the other ranks' memory
-  void close();        // phase 2: free this rank's memory (also runs phase 1 if still needed)
+  // phase 2: free this rank's memory (also runs phase 1 if still needed).  Freeing is only safe once every
+  // importer has unmapped the block, i.e. after the ranks met on the host; a rank that leaves on its own
+  // passes free_own = false and lets process tear-down reclaim the memory.
+  void close(bool free_own = true);
 
   size_t bytes() const { return bytes_; }
   int world() const { return world_; }
@@ -32,6 +35,7 @@ class SymmetricArena {
   size_t bytes_;
   int world_, me_;
   bool opened_ = false, closed_ = false;
+  mutable bool exported_ = false;  // handles were handed out: other processes may map this rank's blocks
   std::vector<void*> data_, flags_;
 };
 

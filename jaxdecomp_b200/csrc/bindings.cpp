@@ -20,6 +20,12 @@
 #include "runtime.h"
 #include "trace.h"
 
+#ifdef JD_BOUNDS_CHECK
+#define JD_BOUNDS_CHECK_BUILD JD_BOUNDS_CHECK
+#else
+#define JD_BOUNDS_CHECK_BUILD 0
+#endif
+
 namespace py = pybind11;
 using namespace jdb;
 
@@ -66,6 +72,9 @@ PYBIND11_MODULE(_jdb200, m) {
   m.attr("BUF_USER_OUT") = (int)BUF_USER_OUT;
   m.attr("BUF_SLOT_A") = (int)BUF_SLOT_A;
   m.attr("BUF_SLOT_B") = (int)BUF_SLOT_B;
+  m.attr("FLAG_EPOCH_COUNTER_WORD") = kFlagEpochCounterWord;
+  m.attr("FLAG_ABORT_WORD") = kFlagAbortWord;
+  m.attr("BOUNDS_CHECK_BUILD") = (bool)JD_BOUNDS_CHECK_BUILD;
   m.def("status_name", [](int s) { return std::string(status_name(s)); });
 
   py::class_<PassDesc>(m, "PassDesc")
@@ -79,7 +88,7 @@ PYBIND11_MODULE(_jdb200, m) {
 #define RW(f) .def_readwrite(#f, &PassDesc::f)
       RW(is_c) RW(is_t) RW(is_o) RW(is_b) RW(os_c) RW(os_t) RW(os_o) RW(os_b) RW(out_base) RW(C) RW(Tn) RW(On) RW(B)
       RW(Cl) RW(Tl) RW(Ol) RW(npeers) RW(fft_mode) RW(M) RW(inverse) RW(T) RW(Cc) RW(pitch) RW(elem_bytes)
-      RW(load_t_contig) RW(store_t_contig) RW(use_bulk) RW(mul_mode) RW(vec_in) RW(vec_out) RW(intra_pad) RW(logT) RW(logW) RW(split_axis) RW(scale)
+      RW(load_t_contig) RW(store_t_contig) RW(use_bulk) RW(mul_mode) RW(vec_in) RW(vec_out) RW(intra_pad) RW(logT) RW(logW) RW(split_axis) RW(scale) RW(grid_limit) RW(out_limit)
 #undef RW
       .def_property("in_ptr", [](const PassDesc& d) { return (uintptr_t)d.in; },
                     [](PassDesc& d, uintptr_t v) { d.in = P(v); })
@@ -96,11 +105,23 @@ PYBIND11_MODULE(_jdb200, m) {
         d.out[p] = P(v);
       })
       .def("get_out", [](const PassDesc& d, int p) { return (uintptr_t)d.out[p]; })
-      .def("copy", [](const PassDesc& d) { return d; });
+      .def("copy", [](const PassDesc& d) { return d; })
+      // the pass restricted to [lo, lo + len) of its t (role 2) or o (role 3) axis; in_ptr must be set
+      .def("restricted", [](const PassDesc& d, int role, int lo, int len) {
+        PassDesc r = d;
+        if (!restrict_pass(r, role, lo, len)) throw py::value_error("pass cannot be restricted to this range");
+        return r;
+      });
 
   m.def("validate_pass", [](const PassDesc& d) { return validate_pass(d); });
   m.def("run_pass_host", [](const PassDesc& d) { raise_on(run_pass_host(d), "run_pass_host"); });
   m.def("launch_pass", [](const PassDesc& d, uintptr_t stream, uintptr_t status) {
+    raise_on(launch_pass(d, P(stream), (StatusBlock*)P(status)), "launch_pass");
+  });
+  // like launch_pass, with the status block also used by the per-store range check of checked builds
+  m.def("launch_pass_checked", [](const PassDesc& d0, uintptr_t stream, uintptr_t status) {
+    PassDesc d = d0;
+    d.status = P(status);
     raise_on(launch_pass(d, P(stream), (StatusBlock*)P(status)), "launch_pass");
   });
   m.def("pass_threads", &pass_threads);
@@ -137,6 +158,9 @@ PYBIND11_MODULE(_jdb200, m) {
       .def_readwrite("out_kind", &PlanStep::out_kind)
       .def_readwrite("copy_only", &PlanStep::copy_only)
       .def_readwrite("copy_bytes", &PlanStep::copy_bytes)
+      .def_readwrite("pipe_chunks", &PlanStep::pipe_chunks)
+      .def_readwrite("pipe_role", &PlanStep::pipe_role)
+      .def_readwrite("pipe_grid_limit", &PlanStep::pipe_grid_limit)
       .def("set_group_ranks", [](PlanStep& s, const std::vector<int>& r) {
         if (r.size() > JD_MAX_PEERS) throw py::value_error("too many peers");
         for (size_t i = 0; i < r.size(); ++i) s.group_ranks[i] = r[i];
@@ -152,7 +176,7 @@ PYBIND11_MODULE(_jdb200, m) {
         r.open_peers(v);
       })
       .def("close_peers", &Runtime::close_peers)
-      .def("destroy_arena", &Runtime::destroy_arena)
+      .def("destroy_arena", &Runtime::destroy_arena, py::arg("collective") = true)
       .def("has_arena", &Runtime::has_arena)
       .def("slot_bytes", &Runtime::slot_bytes)
       .def("slot_ptr", [](const Runtime& r, int slot, int peer) { return (uintptr_t)r.slot_ptr(slot, peer); })
@@ -183,6 +207,9 @@ PYBIND11_MODULE(_jdb200, m) {
         const long long bytes = (long long)B * S0 * S1 * S2 * elem_bytes;
         raise_on(r.halo(dp, du, zero.empty() ? nullptr : &dz, P(src), P(dst), bytes, P(stream)), "halo");
       })
+      .def("set_pipelining", &Runtime::set_pipelining)
+      .def("pipelining", &Runtime::pipelining)
+      .def("pipelined_sections", &Runtime::pipelined_sections)
       .def("barrier", [](Runtime& r, uintptr_t stream) { raise_on(r.barrier(P(stream)), "barrier"); })
       .def("barriers_issued", &Runtime::barriers_issued)
       .def("launches", &Runtime::launches)
@@ -196,6 +223,17 @@ PYBIND11_MODULE(_jdb200, m) {
       .def("wait_only", [](Runtime& r, int n, uint32_t epoch, long long timeout_ms, uintptr_t stream) {
         raise_on(launch_wait_only(r.flag_ptr(r.me()), n, epoch, timeout_ms * 1000000LL, P(stream), r.status_device()),
                  "wait_only");
+      })
+      // test hook: overwrite one 32-bit word of this rank's own flag region (epoch slots, abort word)
+      .def("poke_flag", [](Runtime& r, int word, uint32_t value) {
+        if (word < 0 || word >= 1024) throw py::index_error("flag word");
+        raise_on(r.poke_flag(word, value), "poke_flag");
+      })
+      .def("peek_flag", [](Runtime& r, int word) {
+        if (word < 0 || word >= 1024) throw py::index_error("flag word");
+        uint32_t v = 0;
+        raise_on(r.peek_flag(word, &v), "peek_flag");
+        return v;
       })
       .def_property_readonly("world", &Runtime::world)
       .def_property_readonly("me", &Runtime::me);

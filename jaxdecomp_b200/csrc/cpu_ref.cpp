@@ -8,6 +8,8 @@
 #include <vector>
 
 #include "fft_mixed.h"
+#include <cstdio>
+
 #include "launch.h"
 #include "tile_ops.h"  // also brings fft_core.h
 
@@ -110,9 +112,7 @@ static int run_pass_host_t(const PassDesc& d) {
   return JD_OK;
 }
 
-int run_pass_host(const PassDesc& d) {
-  int rc = validate_pass(d);
-  if (rc != JD_OK) return rc;
+static int run_pass_host_dispatch(const PassDesc& d) {
   if (d.fft_mode == JD_COPY) {
     if (d.elem_bytes == 4) return run_pass_host_t<float>(d);
     if (d.elem_bytes == 8) return run_pass_host_t<cx<float>>(d);
@@ -122,6 +122,27 @@ int run_pass_host(const PassDesc& d) {
   if (d.elem_bytes == 8) return run_pass_host_t<cx<float>>(d);
   if (d.elem_bytes == 16) return run_pass_host_t<cx<double>>(d);
   return JD_ERR_INVALID_ARG;
+}
+
+// The emulation always checks every store against PassDesc::out_limit (tile_ops.h): a store that would
+// leave the destination buffer is skipped and the pass returns JD_ERR_BOUNDS with the first miss in the
+// error message.
+int run_pass_host(const PassDesc& d) {
+  int rc = validate_pass(d);
+  if (rc != JD_OK) return rc;
+  if (pass_aborted(d)) return JD_OK;
+  host_bounds_miss() = BoundsMiss{0, 0, 0, 0};
+  rc = run_pass_host_dispatch(d);
+  if (rc != JD_OK) return rc;
+  const BoundsMiss m = host_bounds_miss();
+  if (m.hit) {
+    char msg[160];
+    std::snprintf(msg, sizeof(msg), "store outside the destination buffer: peer %d, element offset %lld, buffer of %lld elements",
+                  m.peer, m.off, m.limit);
+    set_last_error(msg);
+    return JD_ERR_BOUNDS;
+  }
+  return JD_OK;
 }
 
 // Structural checks shared by the host emulation and the CUDA launcher.

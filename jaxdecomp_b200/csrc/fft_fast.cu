@@ -240,21 +240,16 @@ __device__ __forceinline__ void fast_stage(cx<R>* sm, cx<R>* rowp, int j, int sg
   }
 }
 
-template <typename R, int LOGM, int LOGT, bool STORE_T>
-__global__ void __launch_bounds__((FastCfg<R, LOGM, LOGT, STORE_T>::NT), (FastCfg<R, LOGM, LOGT, STORE_T>::MINB))
-    fft_fast_kernel(const __grid_constant__ PassDesc d) {
-  using Cfg = FastCfg<R, LOGM, LOGT, STORE_T>;
+// One tile: rows [t0, t0 + T) of (o, b).
+template <typename Cfg, typename R>
+__device__ __forceinline__ void fast_tile(const PassDesc& d, cx<R>* sm, int tile, int tiles_t, int tid) {
   using E = cx<R>;
   constexpr int UPR = Cfg::UPR;
-  extern __shared__ __align__(16) unsigned char fast_smem[];
-  E* sm = reinterpret_cast<E*>(fast_smem);
-
-  const int tid = threadIdx.x;
-  const int tiles_t = d.Tn >> LOGT;
-  const int tt = blockIdx.x % tiles_t;
-  const int o = blockIdx.x / tiles_t;
+  constexpr bool STORE_T = Cfg::STORE_T;
+  const int tt = tile % tiles_t;
+  const int o = tile / tiles_t;
   const int b = blockIdx.y;
-  const int t0 = tt << LOGT;
+  const int t0 = tt << Cfg::LOGT;
   const bool inv = d.inverse != 0;
 
   const int j = tid & (UPR - 1);
@@ -289,7 +284,7 @@ __global__ void __launch_bounds__((FastCfg<R, LOGM, LOGT, STORE_T>::NT), (FastCf
       if (inv) v = cswap(v);
       if (do_scale) v = cscale(v, scale);
       const int pc = d.split_axis == 1 ? c / d.Cl : 0;
-      ((E*)d.out[ob.peer + pc + pt])[toff + (c - pc * d.Cl)] = v;
+      store_elem<E>(d, ob.peer + pc + pt, toff + (c - pc * d.Cl), v);
     }
   } else {
     // a[k] now is the result for column j2 + k*M/16 of row row2 (layout of last_stage_map): lanes that
@@ -312,7 +307,38 @@ __global__ void __launch_bounds__((FastCfg<R, LOGM, LOGT, STORE_T>::NT), (FastCf
       E v = a[k];
       if (inv) v = cswap(v);
       if (do_scale) v = cscale(v, scale);
-      ((E*)d.out[ob.peer + pc + pt])[toff + (long long)cl * d.os_c] = v;
+      store_elem<E>(d, ob.peer + pc + pt, toff + (long long)cl * d.os_c, v);
+    }
+  }
+}
+
+// Out-of-line copy of the tile body for the looping variant: as a real call the body gets the same
+// register allocation as the one-tile kernel, and only the loop counters live across it (inlined into
+// the loop, the compiler kept addresses of the next iteration live and spilled up to 190 bytes).
+template <typename Cfg, typename R>
+__device__ __noinline__ void fast_tile_call(const PassDesc& d, cx<R>* sm, int tile, int tiles_t) {
+  fast_tile<Cfg, R>(d, sm, tile, tiles_t, threadIdx.x);
+}
+
+// LOOP = false: one tile per block.  LOOP = true: the grid is smaller than the number of tiles
+// (PassDesc::grid_limit) and every block walks over several tiles, in launch order; such a pass leaves
+// the other SMs to a pass that runs at the same time on another stream.
+template <typename R, int LOGM, int LOGT, bool STORE_T, bool LOOP>
+__global__ void __launch_bounds__((FastCfg<R, LOGM, LOGT, STORE_T>::NT), (FastCfg<R, LOGM, LOGT, STORE_T>::MINB))
+    fft_fast_kernel(const __grid_constant__ PassDesc d) {
+  using Cfg = FastCfg<R, LOGM, LOGT, STORE_T>;
+  extern __shared__ __align__(16) unsigned char fast_smem[];
+  cx<R>* sm = reinterpret_cast<cx<R>*>(fast_smem);
+  if (pass_aborted(d)) return;
+  const int tiles_t = d.Tn >> LOGT;
+  if constexpr (!LOOP) {
+    fast_tile<Cfg, R>(d, sm, blockIdx.x, tiles_t, threadIdx.x);
+  } else {
+    const int ntiles = tiles_t * d.On;
+    for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+      fast_tile_call<Cfg, R>(d, sm, tile, tiles_t);
+      // the next tile's first stage overwrites rows that other threads may still be reading
+      __syncthreads();
     }
   }
 }
@@ -364,9 +390,15 @@ bool fast_pass_eligible(const PassDesc& d) {
 template <typename R, int LOGM, int LOGT, bool STORE_T>
 static int launch_fast_t(const PassDesc& d, cudaStream_t stream) {
   using Cfg = FastCfg<R, LOGM, LOGT, STORE_T>;
-  auto kern = fft_fast_kernel<R, LOGM, LOGT, STORE_T>;
-  static bool configured = false;
-  if (!configured) {
+  const long long nblocks = (long long)(d.Tn >> LOGT) * d.On;
+  if (nblocks > 2147483647LL || d.B > 65535) {
+    set_last_error("fast pass: grid too large");
+    return JD_ERR_INVALID_ARG;
+  }
+  const bool loop = d.grid_limit > 0 && d.grid_limit < nblocks;
+  auto kern = loop ? fft_fast_kernel<R, LOGM, LOGT, STORE_T, true> : fft_fast_kernel<R, LOGM, LOGT, STORE_T, false>;
+  static bool configured[2] = {false, false};
+  if (!configured[loop]) {
     if (Cfg::SMEM > 48 * 1024) {
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM);
       if (e != cudaSuccess) {
@@ -374,14 +406,10 @@ static int launch_fast_t(const PassDesc& d, cudaStream_t stream) {
         return JD_ERR_CUDA;
       }
     }
-    configured = true;
+    configured[loop] = true;
   }
-  const long long nblocks = (long long)(d.Tn >> LOGT) * d.On;
-  if (nblocks > 2147483647LL || d.B > 65535) {
-    set_last_error("fast pass: grid too large");
-    return JD_ERR_INVALID_ARG;
-  }
-  kern<<<dim3((unsigned)nblocks, (unsigned)d.B, 1), Cfg::NT, Cfg::SMEM, stream>>>(d);
+  const long long grid = loop ? d.grid_limit : nblocks;
+  kern<<<dim3((unsigned)grid, (unsigned)d.B, 1), Cfg::NT, Cfg::SMEM, stream>>>(d);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_last_error(cudaGetErrorString(e));

@@ -69,7 +69,7 @@ struct DevStage {
           if (inv) v = cswap(v);
           if (do_scale) v = cscale(v, scale);
           const int pc = d.split_axis == 1 ? c / d.Cl : 0;
-          ((E*)d.out[peer0 + pc])[toff + (c - pc * d.Cl)] = v;
+          store_elem<E>(d, peer0 + pc, toff + (c - pc * d.Cl), v);
         }
       } else {
 #pragma unroll
@@ -87,6 +87,7 @@ __global__ void __launch_bounds__(sizeof(R) == 4 ? 512 : 256, 2)
   E* buf0 = reinterpret_cast<E*>(mixed_smem);
   E* buf1 = buf0 + (size_t)d.T * d.pitch;
 
+  if (pass_aborted(d)) return;
   const int tid = threadIdx.x;
   const int tiles_t = (d.Tn + d.T - 1) / d.T;
   const int tt = blockIdx.x % tiles_t;

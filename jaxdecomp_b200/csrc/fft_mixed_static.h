@@ -88,9 +88,9 @@ __device__ __forceinline__ void static_stage(const PassDesc& d, const cx<R>* __r
         const int pc = d.split_axis == 1 ? (int)__umulhi((uint32_t)c, clm) : 0;
         const int cl = c - pc * d.Cl;
         if constexpr (ROT) {
-          ((E*)d.out[peer0 + pc])[toff + (long long)cl * d.os_c] = v;
+          store_elem<E>(d, peer0 + pc, toff + (long long)cl * d.os_c, v);
         } else {
-          ((E*)d.out[peer0 + pc])[toff + cl] = v;
+          store_elem<E>(d, peer0 + pc, toff + cl, v);
         }
       }
     } else if constexpr (LS % 16 == 0) {
@@ -148,6 +148,7 @@ __global__ void __launch_bounds__((MixedCfg<R, N, T, DOUT>::NT), (MixedCfg<R, N,
   E* buf0 = reinterpret_cast<E*>(mixed_static_smem);
   E* buf1 = buf0 + (size_t)T * Cfg::PITCH;
 
+  if (pass_aborted(d)) return;
   const int tid = threadIdx.x;
   const int tiles_t = (d.Tn + T - 1) / T;
   const int tt = blockIdx.x % tiles_t;

@@ -157,6 +157,7 @@ __global__ void __launch_bounds__(FFT ? (sizeof(E) == 16 ? 256 : 512) : 256,
   extern __shared__ __align__(128) unsigned char smem_raw[];
   __shared__ uint64_t bar;
   E* tile = (E*)smem_raw;
+  if (pass_aborted(d)) return;
 
   const int tiles_t = (d.Tn + d.T - 1) / d.T;
   const int tiles_c = FFT ? 1 : (d.C + d.Cc - 1) / d.Cc;

@@ -28,6 +28,10 @@ int launch_mixed_static_b(const PassDesc& d, void* stream);
 int launch_mixed_static_c(const PassDesc& d, void* stream);
 
 // ---- cross-rank signalling (signal.cu) ---------------------------------------------------------------
+// Words of a rank's flag region (uint32): [0, JD_MAX_PEERS) epoch slots, one per peer; the rank's own
+// barrier counter; the abort word (0, or 1 + the rank whose wait failed).
+constexpr int kFlagEpochCounterWord = 64;
+constexpr int kFlagAbortWord = 65;
 struct PeerFlags {
   uint32_t* flags[JD_MAX_PEERS];  // flags[p]: base of peer p's flag array (its own for p == me)
 };

@@ -5,23 +5,26 @@
 
 #include <cstdio>
 #include <stdexcept>
+#include <vector>
 
 #include "trace.h"
 
 namespace jdb {
 
-// flag region layout (uint32 words): [0, JD_MAX_PEERS) epoch slots, word 64: this rank's epoch counter
-static constexpr int kEpochCounterWord = 64;
+static constexpr int kEpochCounterWord = kFlagEpochCounterWord;
 
 Runtime::Runtime(int world, int me) : world_(world), me_(me) {
   if (world < 1 || world > JD_MAX_PEERS || me < 0 || me >= world) throw std::runtime_error("runtime: bad world/rank");
   JD_TRACE_INFO("runtime", "create world=%d rank=%d", world, me);
 }
 
-Runtime::~Runtime() { destroy_arena(); }
+Runtime::~Runtime() {
+  release_pipe_resources();
+  destroy_arena(false);
+}
 
 void Runtime::create_arena(size_t slot_bytes) {
-  destroy_arena();
+  destroy_arena(true);  // regrowth is collective: the caller closed the peers' handles and met them on the host
   if (!status_) status_.reset(new HostStatus());
   // round the slot so that the second slot stays 2 MiB aligned
   const size_t gran = (size_t)2 << 20;
@@ -47,10 +50,10 @@ void Runtime::close_peers() {
   if (arena_) arena_->close_peers();
 }
 
-void Runtime::destroy_arena() {
+void Runtime::destroy_arena(bool collective) {
   if (arena_) {
-    JD_TRACE_INFO("runtime", "arena destroyed");
-    arena_->close();
+    JD_TRACE_INFO("runtime", "arena destroyed (%s)", collective ? "collective" : "local: exported blocks kept");
+    arena_->close(collective);
     arena_.reset();
   }
   slot_bytes_ = 0;
@@ -111,6 +114,188 @@ int Runtime::barrier(void* stream) {
                                status_device());
 }
 
+// ---- plan execution ------------------------------------------------------------------------------------
+// Hazards between steps are tracked per arena slot with the count of barriers issued so far (identical
+// on every rank, because all ranks issue the same sequence): a slot that peers wrote since the last
+// barrier must not be read, and a slot that this rank read since the last barrier must not be written by
+// peers, before another barrier has passed.
+int Runtime::sync_before(const PlanStep& st, void* stream) {
+  if (world_ <= 1) return JD_OK;
+  const int is = st.in_kind - BUF_SLOT_A, os = st.out_kind - BUF_SLOT_A;
+  // read-after-remote-write: everybody's stores into the slot must have landed
+  if (is >= 0 && slot_written_[is] == host_epoch_) {
+    int rc = barrier(stream);
+    if (rc != JD_OK) return rc;
+  }
+  // write-after-read: nobody may still be reading the slot from an earlier step
+  if (os >= 0 && slot_read_[os] == host_epoch_) {
+    int rc = barrier(stream);
+    if (rc != JD_OK) return rc;
+  }
+  return JD_OK;
+}
+
+void Runtime::fill_pointers(const PlanStep& st, PassDesc& d, const void* in, void* out) const {
+  const int is = st.in_kind - BUF_SLOT_A, os = st.out_kind - BUF_SLOT_A;
+  d.in = st.in_kind == BUF_USER_IN ? in : (st.in_kind == BUF_USER_OUT ? out : slot_ptr(is, me_));
+  for (int p = 0; p < d.npeers; ++p) d.out[p] = st.out_kind == BUF_USER_OUT ? out : slot_ptr(os, st.group_ranks[p]);
+  d.abort_word = (arena_ && world_ > 1) ? flag_ptr(me_) + kFlagAbortWord : nullptr;
+  d.status = status_device();
+}
+
+// Launch step `index` of the plan (or, when chunk_desc is given, that restricted copy of its descriptor,
+// whose pointers are already set) on `stream`.
+int Runtime::launch_step(const Plan& pl, int plan_id, size_t index, const PassDesc* chunk_desc, const void* in,
+                         void* out, void* stream) {
+  const PlanStep& st = pl.steps[index];
+  const int is = st.in_kind - BUF_SLOT_A, os = st.out_kind - BUF_SLOT_A;
+  if (st.copy_only) {
+    const void* src = st.in_kind == BUF_USER_IN ? in : (st.in_kind == BUF_USER_OUT ? out : slot_ptr(is, me_));
+    void* dst = st.out_kind == BUF_USER_OUT ? out : slot_ptr(os, me_);
+    cudaError_t e = cudaMemcpyAsync(dst, src, (size_t)st.copy_bytes, cudaMemcpyDeviceToDevice, (cudaStream_t)stream);
+    if (e != cudaSuccess) {
+      set_last_error(cudaGetErrorString(e));
+      return JD_ERR_CUDA;
+    }
+  } else if (chunk_desc != nullptr) {
+    int rc = launch_pass(*chunk_desc, stream, status_device());
+    if (rc != JD_OK) return rc;
+  } else {
+    PassDesc d = st.desc;
+    fill_pointers(st, d, in, out);
+    int rc = launch_pass(d, stream, status_device());
+    if (rc != JD_OK) return rc;
+  }
+  ++launches_;
+  (void)plan_id;
+  return JD_OK;
+}
+
+int Runtime::ensure_pipe_resources(int chunks) {
+  auto fail = [](cudaError_t e) {
+    set_last_error(cudaGetErrorString(e));
+    return (int)JD_ERR_CUDA;
+  };
+  if (!side_stream_) {
+    int lo = 0, hi = 0;
+    cudaError_t e = cudaDeviceGetStreamPriorityRange(&lo, &hi);
+    if (e != cudaSuccess) return fail(e);
+    cudaStream_t s;
+    e = cudaStreamCreateWithPriority(&s, cudaStreamNonBlocking, hi);
+    if (e != cudaSuccess) return fail(e);
+    side_stream_ = s;
+    cudaEvent_t ev;
+    e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
+    if (e != cudaSuccess) return fail(e);
+    fork_event_ = ev;
+  }
+  while ((int)chunk_events_.size() < chunks) {
+    cudaEvent_t ev;
+    cudaError_t e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
+    if (e != cudaSuccess) return fail(e);
+    chunk_events_.push_back(ev);
+  }
+  return JD_OK;
+}
+
+void Runtime::release_pipe_resources() {
+  for (void* ev : chunk_events_) cudaEventDestroy((cudaEvent_t)ev);
+  chunk_events_.clear();
+  if (fork_event_) cudaEventDestroy((cudaEvent_t)fork_event_);
+  if (side_stream_) cudaStreamDestroy((cudaStream_t)side_stream_);
+  fork_event_ = side_stream_ = nullptr;
+  cudaGetLastError();
+}
+
+// Steps index (an exchange pass) and index + 1 (the local pass that consumes it), cut into chunks.
+// The exchange chunks run back to back on a high-priority side stream, so the link never waits for
+// the local pass; the caller's stream runs, per chunk: wait for this rank's chunk to be issued, a
+// cross-rank barrier ("chunk k of every rank has landed"), the local pass on chunk k.  All barriers of
+// the section are on the caller's stream, so the ranks keep counting the same barriers in the same
+// order.  The side stream is joined again by the last event the caller's stream waits for, which also
+// makes the section capturable in a CUDA graph.
+int Runtime::run_pipelined(Plan& pl, int plan_id, size_t index, const void* in, void* out, void* stream) {
+  PlanStep& prod = pl.steps[index];
+  PlanStep& cons = pl.steps[index + 1];
+  const int K = prod.pipe_chunks;
+  int rc = ensure_pipe_resources(K);
+  if (rc != JD_OK) return rc;
+  // hazards of both steps are settled up front, on the caller's stream
+  if ((rc = sync_before(prod, stream)) != JD_OK) return rc;
+  const int cos = cons.out_kind - BUF_SLOT_A;
+  if (cos >= 0 && slot_read_[cos] == host_epoch_ && (rc = barrier(stream)) != JD_OK) return rc;
+
+  PassDesc pd = prod.desc, cd = cons.desc;
+  fill_pointers(prod, pd, in, out);
+  fill_pointers(cons, cd, in, out);
+  pd.grid_limit = prod.pipe_grid_limit;
+  const int pext = prod.pipe_role == 2 ? pd.Tn : pd.On;
+  const int cext = cons.pipe_role == 2 ? cd.Tn : cd.On;
+  if (pext != cext || K < 2 || pext % K) {
+    set_last_error("runtime: inconsistent pipeline annotation in plan");
+    return JD_ERR_INVALID_ARG;
+  }
+  const int len = pext / K;
+  std::vector<PassDesc> pchunk(K, pd), cchunk(K, cd);
+  for (int k = 0; k < K; ++k)
+    if (!restrict_pass(pchunk[k], prod.pipe_role, k * len, len) || !restrict_pass(cchunk[k], cons.pipe_role, k * len, len)) {
+      set_last_error("runtime: pass cannot be cut into the requested chunks");
+      return JD_ERR_INVALID_ARG;
+    }
+
+  StepProfiler& prof = StepProfiler::instance();
+  const bool profiling = prof.mode() != StepProfiler::OFF;
+  if (profiling) {
+    char name[96];
+    std::snprintf(name, sizeof(name), "plan%d.step%d+%d pipelined x%d", plan_id, (int)index, (int)index + 1, K);
+    prof.start(name, stream);
+  }
+  cudaStream_t main_s = (cudaStream_t)stream, side = (cudaStream_t)side_stream_;
+  auto cuda_ok = [](cudaError_t e) {
+    if (e == cudaSuccess) return true;
+    set_last_error(cudaGetErrorString(e));
+    return false;
+  };
+  if (!cuda_ok(cudaEventRecord((cudaEvent_t)fork_event_, main_s)) ||
+      !cuda_ok(cudaStreamWaitEvent(side, (cudaEvent_t)fork_event_, 0)))
+    return JD_ERR_CUDA;
+  auto issue_exchange = [&](int k) -> int {
+    int r = launch_step(pl, plan_id, index, &pchunk[k], in, out, side);
+    if (r != JD_OK) return r;
+    return cuda_ok(cudaEventRecord((cudaEvent_t)chunk_events_[k], side)) ? (int)JD_OK : (int)JD_ERR_CUDA;
+  };
+  // Whatever happens below, the caller's stream must join the side stream again (a captured graph
+  // would otherwise be left with an unjoined branch), so errors are remembered, not returned at once.
+  int first_err = issue_exchange(0);
+  int issued = first_err == JD_OK ? 1 : 0;
+  for (int k = 0; k < K && first_err == JD_OK; ++k) {
+    if (k + 1 < K) {
+      first_err = issue_exchange(k + 1);
+      if (first_err != JD_OK) break;
+      ++issued;
+    }
+    if (!cuda_ok(cudaStreamWaitEvent(main_s, (cudaEvent_t)chunk_events_[k], 0))) {
+      first_err = JD_ERR_CUDA;
+      break;
+    }
+    if ((first_err = barrier(stream)) != JD_OK) break;
+    first_err = launch_step(pl, plan_id, index + 1, &cchunk[k], in, out, stream);
+  }
+  if (issued > 0) cudaStreamWaitEvent(main_s, (cudaEvent_t)chunk_events_[issued - 1], 0);
+  if (profiling) prof.stop(stream);
+  if (first_err != JD_OK) return first_err;
+  ++pipelined_sections_;
+  // the exchange slot was written before the section's last barrier and read after it
+  const int pos = prod.out_kind - BUF_SLOT_A, pis = prod.in_kind - BUF_SLOT_A;
+  if (pis >= 0) slot_read_[pis] = host_epoch_;
+  if (pos >= 0) {
+    slot_written_[pos] = host_epoch_ - 1;
+    slot_read_[pos] = host_epoch_;
+  }
+  if (cos >= 0) slot_written_[cos] = host_epoch_;
+  return JD_OK;
+}
+
 int Runtime::execute(int plan_id, const void* in, void* out, void* stream) {
   Plan& pl = plans_.at(plan_id);
   if (world_ > 1 || pl.slot_bytes > 0) {
@@ -119,51 +304,31 @@ int Runtime::execute(int plan_id, const void* in, void* out, void* stream) {
       return JD_ERR_INVALID_ARG;
     }
   }
-  for (PlanStep& st : pl.steps) {
-    const int is = st.in_kind - BUF_SLOT_A, os = st.out_kind - BUF_SLOT_A;
-    // read-after-remote-write: everybody's stores into the slot must have landed
-    if (is >= 0 && slot_written_[is] == host_epoch_ && world_ > 1) {
-      int rc = barrier(stream);
+  StepProfiler& prof = StepProfiler::instance();
+  for (size_t i = 0; i < pl.steps.size(); ++i) {
+    PlanStep& st = pl.steps[i];
+    if (st.pipe_chunks > 1 && pipelining_ && world_ > 1 && i + 1 < pl.steps.size() && !st.copy_only) {
+      int rc = run_pipelined(pl, plan_id, i, in, out, stream);
       if (rc != JD_OK) return rc;
+      ++i;
+      continue;
     }
-    // write-after-read: nobody may still be reading the slot from an earlier step
-    if (os >= 0 && slot_read_[os] == host_epoch_ && world_ > 1) {
-      int rc = barrier(stream);
-      if (rc != JD_OK) return rc;
-    }
-    const void* src = st.in_kind == BUF_USER_IN ? in : (st.in_kind == BUF_USER_OUT ? out : slot_ptr(is, me_));
-    StepProfiler& prof = StepProfiler::instance();
+    int rc = sync_before(st, stream);
+    if (rc != JD_OK) return rc;
     const bool profiling = prof.mode() != StepProfiler::OFF;
     if (profiling) {
       char name[96];
       if (st.copy_only)
-        std::snprintf(name, sizeof(name), "plan%d.step%d copy", plan_id, (int)(&st - &pl.steps[0]));
+        std::snprintf(name, sizeof(name), "plan%d.step%d copy", plan_id, (int)i);
       else
-        std::snprintf(name, sizeof(name), "plan%d.step%d %s C=%d peers=%d", plan_id, (int)(&st - &pl.steps[0]),
+        std::snprintf(name, sizeof(name), "plan%d.step%d %s C=%d peers=%d", plan_id, (int)i,
                       st.desc.fft_mode == JD_COPY ? "copy-pass" : "fft-pass", st.desc.C, st.desc.npeers);
       prof.start(name, stream);
     }
-    if (st.copy_only) {
-      void* dst = st.out_kind == BUF_USER_OUT ? out : slot_ptr(os, me_);
-      cudaError_t e = cudaMemcpyAsync(dst, src, (size_t)st.copy_bytes, cudaMemcpyDeviceToDevice, (cudaStream_t)stream);
-      if (e != cudaSuccess) {
-        set_last_error(cudaGetErrorString(e));
-        return JD_ERR_CUDA;
-      }
-    } else {
-      PassDesc d = st.desc;
-      d.in = src;
-      for (int p = 0; p < d.npeers; ++p) {
-        if (st.out_kind == BUF_USER_OUT)
-          d.out[p] = out;
-        else
-          d.out[p] = slot_ptr(os, st.group_ranks[p]);
-      }
-      int rc = launch_pass(d, stream, status_device());
-      if (rc != JD_OK) return rc;
-    }
+    rc = launch_step(pl, plan_id, i, nullptr, in, out, stream);
     if (profiling) prof.stop(stream);
-    ++launches_;
+    if (rc != JD_OK) return rc;
+    const int is = st.in_kind - BUF_SLOT_A, os = st.out_kind - BUF_SLOT_A;
     if (is >= 0) slot_read_[is] = host_epoch_;
     if (os >= 0) slot_written_[os] = host_epoch_;
   }
@@ -209,6 +374,28 @@ int Runtime::halo(HaloDesc pack, HaloDesc unpack, const HaloDesc* zero, const vo
   if ((rc = launch_halo_unpack(unpack, stream)) != JD_OK) return rc;
   ++launches_;
   slot_read_[slot] = host_epoch_;
+  return JD_OK;
+}
+
+int Runtime::poke_flag(int word, uint32_t value) {
+  if (!arena_) return JD_ERR_INVALID_ARG;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e == cudaSuccess) e = cudaMemcpy(flag_ptr(me_) + word, &value, sizeof(value), cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) {
+    set_last_error(cudaGetErrorString(e));
+    return JD_ERR_CUDA;
+  }
+  return JD_OK;
+}
+
+int Runtime::peek_flag(int word, uint32_t* value) const {
+  if (!arena_) return JD_ERR_INVALID_ARG;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e == cudaSuccess) e = cudaMemcpy(value, flag_ptr(me_) + word, sizeof(*value), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) {
+    set_last_error(cudaGetErrorString(e));
+    return JD_ERR_CUDA;
+  }
   return JD_OK;
 }
 

@@ -43,6 +43,13 @@ struct PlanStep {
   int32_t copy_only = 0;       // 1: plain device-to-device copy of copy_bytes from in to out
   long long copy_bytes = 0;
   int32_t group_ranks[JD_MAX_PEERS] = {0};  // arena rank of destination peer p (npeers entries)
+  // Pipelining with the next step (set on an exchange pass that is followed by a local pass): the pass
+  // is cut into pipe_chunks chunks along its axis pipe_role (2 = t, 3 = o); the next step is cut the same
+  // way along its own pipe_role, and chunk k of the next step starts as soon as chunk k of this step has
+  // arrived from every rank, while chunk k + 1 is still crossing NVLink.
+  int32_t pipe_chunks = 0;
+  int32_t pipe_role = 0;
+  int32_t pipe_grid_limit = 0;  // blocks of each chunk of the exchange pass (0: one per tile)
 };
 
 struct Plan {
@@ -61,7 +68,9 @@ class Runtime {
   std::string export_handles() const;
   void open_peers(const std::vector<std::string>& handles);
   void close_peers();   // collective tear-down, phase 1 (host barrier needed before destroy_arena)
-  void destroy_arena();
+  // collective = true: the caller guarantees that every rank ran close_peers() and the ranks then met on the
+  // host, so the exported blocks can be freed; false: a rank leaving alone only unmaps its imports.
+  void destroy_arena(bool collective = true);
   size_t slot_bytes() const { return slot_bytes_; }
   bool has_arena() const { return (bool)arena_; }
   void* slot_ptr(int slot, int peer) const;
@@ -78,6 +87,10 @@ class Runtime {
 
   // execution
   int execute(int plan_id, const void* in, void* out, void* stream);
+  // 0 disables the pipelined execution of plans (every step then runs in order on the caller's stream)
+  void set_pipelining(bool on) { pipelining_ = on; }
+  bool pipelining() const { return pipelining_; }
+  long long pipelined_sections() const { return pipelined_sections_; }
   int barrier(void* stream);
   // pack -> (zero fill) -> barrier -> unpack through arena slot 0; copies src to dst first when they differ
   int halo(HaloDesc pack, HaloDesc unpack, const HaloDesc* zero, const void* src, void* dst, long long bytes,
@@ -90,6 +103,10 @@ class Runtime {
   void clear_status();
   StatusBlock* status_device() const { return status_ ? status_->device() : nullptr; }
 
+  // synchronous access to one word of this rank's flag region (tests of the stale-epoch and abort paths)
+  int poke_flag(int word, uint32_t value);
+  int peek_flag(int word, uint32_t* value) const;
+
   void set_timeout_ms(long long ms) { timeout_ns_ = ms * 1000000LL; }
   int world() const { return world_; }
   int me() const { return me_; }
@@ -99,7 +116,7 @@ class Runtime {
   std::unique_ptr<SymmetricArena> arena_;
   std::unique_ptr<HostStatus> status_;
   size_t slot_bytes_ = 0;
-  long long timeout_ns_ = 2000000000LL;
+  long long timeout_ns_ = 10000000000LL;
   // hazard tracking (identical on every rank because all ranks issue the same sequence)
   long long host_epoch_ = 0;
   long long slot_written_[2] = {-1, -1};  // epoch during which peers last wrote the slot
@@ -107,6 +124,19 @@ class Runtime {
   std::map<std::string, int> plan_index_;
   std::vector<Plan> plans_;
   long long hits_ = 0, misses_ = 0, launches_ = 0;
+  // pipelined execution: one extra high-priority stream for the exchange chunks and one event per chunk
+  bool pipelining_ = true;
+  long long pipelined_sections_ = 0;
+  void* side_stream_ = nullptr;
+  void* fork_event_ = nullptr;
+  std::vector<void*> chunk_events_;
+  int ensure_pipe_resources(int chunks);
+  void release_pipe_resources();
+  int sync_before(const PlanStep& st, void* stream);
+  int launch_step(const Plan& pl, int plan_id, size_t index, const PassDesc* chunk_desc, const void* in, void* out,
+                  void* stream);
+  void fill_pointers(const PlanStep& st, PassDesc& d, const void* in, void* out) const;
+  int run_pipelined(Plan& pl, int plan_id, size_t index, const void* in, void* out, void* stream);
 };
 
 }  // namespace jdb

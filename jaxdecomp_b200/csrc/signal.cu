@@ -10,7 +10,9 @@
 // value >= e (acquire, system scope).  Epochs only grow, so slots are never
 // reset.  The wait is bounded by a wall-clock budget read from %globaltimer;
 // when it expires the kernel records {TIMEOUT_PEER_SIGNAL, peer, expected,
-// seen} in the status block and returns normally.  It never traps or spins forever.
+// seen} in the status block, sets the abort word of every rank (so that no
+// pass runs on incomplete data and every rank raises) and returns normally.
+// It never traps or spins forever.
 #include <cuda_runtime.h>
 
 #include "launch.h"
@@ -31,23 +33,49 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   return v;
 }
 
-__device__ void bounded_wait(const uint32_t* slot, uint32_t epoch, long long timeout_ns, int peer, StatusBlock* st) {
+// Result of a bounded wait: 0 when the slot reached the epoch, else the Status that ended it.
+//   * TIMEOUT_PEER_SIGNAL: the wall-clock budget ran out;
+//   * STALE_EPOCH: the slot is more than one barrier ahead of the epoch waited for.  A peer signals
+//     barrier e+1 only after it left barrier e, and it cannot leave barrier e+1 before this rank
+//     signalled e+1, so a healthy slot is never ahead by more than one: a larger lead means that the
+//     ranks no longer count the same barriers (a replayed or skipped barrier, a corrupted slot);
+//   * PEER_ABORTED: the rank's abort word was set by a peer whose own wait failed.
+__device__ int bounded_wait(const uint32_t* slot, uint32_t epoch, long long timeout_ns, const uint32_t* abort_word,
+                            uint32_t* seen_out) {
   const unsigned long long t0 = globaltimer_ns();
   uint32_t seen = 0;
   unsigned spins = 0;
+  int rc = JD_ERR_TIMEOUT_PEER_SIGNAL;
   for (;;) {
     seen = ld_acquire_sys(slot);
-    if ((int32_t)(seen - epoch) >= 0) return;
+    const int32_t lead = (int32_t)(seen - epoch);
+    if (lead > 1) {
+      rc = JD_ERR_STALE_EPOCH;
+      break;
+    }
+    if (lead >= 0) {
+      rc = JD_OK;
+      break;
+    }
     if ((++spins & 15u) == 0) {
+      if (abort_word != nullptr && ld_acquire_sys(abort_word) != 0) {
+        rc = JD_ERR_PEER_ABORTED;
+        break;
+      }
       if ((long long)(globaltimer_ns() - t0) > timeout_ns) break;
       __nanosleep(100);
     }
   }
-  if (st != nullptr && atomicCAS(&st->code, 0, (int)JD_ERR_TIMEOUT_PEER_SIGNAL) == 0) {
+  *seen_out = seen;
+  return rc;
+}
+
+__device__ void record_status(StatusBlock* st, int code, int peer, uint32_t expected, uint32_t seen, int where) {
+  if (st != nullptr && atomicCAS(&st->code, 0, code) == 0) {
     st->peer = peer;
-    st->expected = (int32_t)epoch;
+    st->expected = (int32_t)expected;
     st->seen = (int32_t)seen;
-    st->where = 100;
+    st->where = where;
     __threadfence_system();
   }
 }
@@ -55,6 +83,7 @@ __device__ void bounded_wait(const uint32_t* slot, uint32_t epoch, long long tim
 __global__ void signal_barrier_kernel(PeerFlags pf, int me, int n, uint32_t* epoch_counter, uint32_t epoch_arg,
                                       long long timeout_ns, StatusBlock* st) {
   const int p = threadIdx.x;
+  uint32_t* abort_word = pf.flags[me] + kFlagAbortWord;
   // The epoch normally lives in device memory and is advanced by the barrier
   // itself, so that a captured CUDA graph can be replayed: every rank runs the
   // same sequence of barriers and therefore counts identically.
@@ -64,18 +93,35 @@ __global__ void signal_barrier_kernel(PeerFlags pf, int me, int n, uint32_t* epo
     __syncwarp();
     if (p == 0) *epoch_counter = epoch;
   }
+  // A rank whose wait failed earlier (here or on a peer) takes no further part: its kernels return at
+  // entry, it signals nothing, and the host raises at its next status check.
+  const uint32_t aborted = ld_acquire_sys(abort_word);
+  if (aborted != 0) {
+    if (p == 0) record_status(st, JD_ERR_PEER_ABORTED, (int)aborted - 1, epoch, 0, 101);
+    return;
+  }
   if (p >= n) return;
   // everything this stream did before (including peer stores of the previous
   // kernel) is ordered before the flag
   __threadfence_system();
   st_release_sys(pf.flags[p] + me, epoch);
-  bounded_wait(pf.flags[me] + p, epoch, timeout_ns, p, st);
+  uint32_t seen = 0;
+  const int rc = bounded_wait(pf.flags[me] + p, epoch, timeout_ns, abort_word, &seen);
+  if (rc != JD_OK) {
+    record_status(st, rc, rc == JD_ERR_PEER_ABORTED ? (int)ld_acquire_sys(abort_word) - 1 : p, epoch, seen, 100);
+    // The data this barrier was guarding is incomplete.  Mark this rank and every peer as aborted so
+    // that no later pass computes on it and no rank returns a result as if nothing had happened.
+    if (rc != JD_ERR_PEER_ABORTED)
+      for (int q = 0; q < n; ++q) st_release_sys(pf.flags[q] + kFlagAbortWord, (uint32_t)me + 1);
+  }
 }
 
 __global__ void wait_only_kernel(uint32_t* my_flags, int n, uint32_t epoch, long long timeout_ns, StatusBlock* st) {
   const int p = threadIdx.x;
   if (p >= n) return;
-  bounded_wait(my_flags + p, epoch, timeout_ns, p, st);
+  uint32_t seen = 0;
+  const int rc = bounded_wait(my_flags + p, epoch, timeout_ns, nullptr, &seen);
+  if (rc != JD_OK) record_status(st, rc, p, epoch, seen, 100);
 }
 
 static int check_launch() {

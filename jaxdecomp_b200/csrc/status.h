@@ -16,10 +16,11 @@ enum Status : int32_t {
   JD_ERR_INVALID_ARG = -1,
   JD_ERR_CUDA = -2,
   JD_ERR_TIMEOUT_PEER_SIGNAL = -3,  // bounded wait on a peer's flag expired
-  JD_ERR_STALE_EPOCH = -4,          // a flag carried an epoch from the future/past
+  JD_ERR_STALE_EPOCH = -4,          // a flag is more than one barrier ahead of the epoch waited for
   JD_ERR_BOUNDS = -5,               // debug bounds check failed; access skipped
   JD_ERR_TIMEOUT_MBARRIER = -6,     // bounded wait on a local bulk-copy barrier expired
   JD_ERR_UNSUPPORTED = -7,
+  JD_ERR_PEER_ABORTED = -8,         // a peer's bounded wait failed and it marked the whole group as aborted
 };
 
 inline const char* status_name(int32_t s) {
@@ -33,6 +34,7 @@ inline const char* status_name(int32_t s) {
     case JD_ERR_BOUNDS: return "BOUNDS";
     case JD_ERR_TIMEOUT_MBARRIER: return "TIMEOUT_MBARRIER";
     case JD_ERR_UNSUPPORTED: return "UNSUPPORTED";
+    case JD_ERR_PEER_ABORTED: return "PEER_ABORTED";
     default: return "UNKNOWN";
   }
 }

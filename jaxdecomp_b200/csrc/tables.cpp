@@ -79,6 +79,7 @@ static void* upload(const std::vector<cld>& v, int elem_bytes, bool device) {
 }
 
 struct TableSet {
+  int ordinal = -1;  // GPU that owns the device copies
   void* twiddle = nullptr;
   void* tw_stage = nullptr;
   void* chirp = nullptr;
@@ -87,7 +88,9 @@ struct TableSet {
 };
 
 static std::mutex g_mu;
-static std::map<std::tuple<int, int, int, bool>, TableSet> g_tables;  // (C, M, elem_bytes, device)
+// (C, M, elem_bytes, device ordinal or -1 for host tables): device tables live in the memory of the GPU that
+// was current when they were built, so every GPU of a multi-device process gets its own set
+static std::map<std::tuple<int, int, int, int>, TableSet> g_tables;
 
 FftTables get_fft_tables(int C, int M, int elem_bytes, bool device) {
   if (elem_bytes != 8 && elem_bytes != 16) throw std::runtime_error("tables: complex64/complex128 only");
@@ -95,11 +98,17 @@ FftTables get_fft_tables(int C, int M, int elem_bytes, bool device) {
   if (C != M && (M < 8 || (M & (M - 1)))) throw std::runtime_error("tables: M must be a power of two >= 8");
   if (M < 1) throw std::runtime_error("tables: empty table");
   std::lock_guard<std::mutex> lk(g_mu);
-  auto key = std::make_tuple(C, M, elem_bytes, device);
+  int ordinal = -1;
+  if (device && cudaGetDevice(&ordinal) != cudaSuccess) {
+    cudaGetLastError();
+    throw std::runtime_error("tables: no current CUDA device");
+  }
+  auto key = std::make_tuple(C, M, elem_bytes, ordinal);
   auto it = g_tables.find(key);
   if (it == g_tables.end()) {
     TableSet ts;
     ts.device = device;
+    ts.ordinal = ordinal;
     std::vector<cld> tw(M);
     for (int n = 0; n < M; ++n) {
       const long double ang = -2.0L * kPi * (long double)n / (long double)M;
@@ -165,8 +174,11 @@ FftTables get_fft_tables(int C, int M, int elem_bytes, bool device) {
 
 void clear_fft_tables() {
   std::lock_guard<std::mutex> lk(g_mu);
+  int cur = -1;
+  cudaGetDevice(&cur);
   for (auto& kv : g_tables) {
     TableSet& ts = kv.second;
+    if (ts.device && ts.ordinal >= 0) cudaSetDevice(ts.ordinal);
     for (void* p : {ts.twiddle, ts.tw_stage, ts.chirp, ts.bhat}) {
       if (!p) continue;
       if (ts.device)
@@ -176,6 +188,7 @@ void clear_fft_tables() {
     }
   }
   g_tables.clear();
+  if (cur >= 0) cudaSetDevice(cur);
   cudaGetLastError();
 }
 

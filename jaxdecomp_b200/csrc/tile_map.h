@@ -65,6 +65,8 @@ struct PassDesc {
   int32_t logT;           // T == 1 << logT
   int32_t logW;           // columns held per row (M in fft modes, Cc in copy mode) == 1 << logW
   int32_t split_axis;     // which axis selects the peer: 0 none, 1 c, 2 t, 3 o
+  int32_t grid_limit;     // > 0: launch at most this many blocks, each looping over tiles (leaves the other
+                          // SMs to a pass that runs concurrently on another stream); 0: one block per tile
   double scale;
   const void* in;
   void* out[JD_MAX_PEERS];
@@ -73,6 +75,11 @@ struct PassDesc {
   const void* chirp;      // Bluestein: C entries exp(-i*pi*n^2/C)
   const void* bhat;       // Bluestein: M entries FFT_M(conj chirp, wrapped) / M
   const void* mul;        // reserved (see mul_mode); must be null
+  const uint32_t* abort_word;  // device word of this rank that a failed cross-rank wait sets (signal.cu); blocks
+                               // return at entry when it is non-zero; null: not checked
+  long long out_limit;    // elements each destination buffer holds; checked per store by the CPU emulation and by
+                          // kernels compiled with JD_BOUNDS_CHECK (0: unknown, not checked)
+  void* status;           // StatusBlock* for the bounds check of JD_BOUNDS_CHECK builds, or null
 };
 
 // (c, t, o, b) of the local block -> destination peer and element offset there.
@@ -81,6 +88,35 @@ JD_HD void out_location(const PassDesc& d, int c, int t, int o, int b, int& peer
   peer = pc + pt + po;
   off = d.out_base + (long long)(c - pc * d.Cl) * d.os_c + (long long)(t - pt * d.Tl) * d.os_t +
         (long long)(o - po * d.Ol) * d.os_o + (long long)b * d.os_b;
+}
+
+// Restrict a pass to the rows [lo, lo + len) of its t axis (role == 2) or its o axis (role == 3).
+// The restricted pass reads and writes exactly the elements that the full pass touches for those
+// indices, so running it for a partition of the axis is equivalent to the full pass.  Used to cut a
+// pass into chunks that are pipelined with the pass that consumes them.  Requirements: the axis must
+// not select the destination peer, and a t range must start and end on a tile boundary (so that tiles,
+// and with them the vector-access alignment rules, are those of the full pass).  The pointer `in`
+// must already be set.  Returns false (descriptor unchanged) when the range is not admissible.
+inline bool restrict_pass(PassDesc& d, int role, int lo, int len) {
+  if (role != 2 && role != 3) return false;
+  if (d.split_axis == role || lo < 0 || len <= 0) return false;
+  const int ext = role == 2 ? d.Tn : d.On;
+  if (lo + len > ext) return false;
+  if (role == 2) {
+    // tile heights are powers of two up to 32 (the specialised kernels pick theirs from Tn's divisibility)
+    const int align = d.T > 32 ? d.T : 32;
+    if ((lo % align) != 0 || ((len % align) != 0 && lo + len != ext)) return false;
+    d.in = static_cast<const char*>(d.in) + (long long)lo * d.is_t * d.elem_bytes;
+    d.out_base += (long long)lo * d.os_t;
+    d.Tn = len;
+    d.Tl = len;
+  } else {
+    d.in = static_cast<const char*>(d.in) + (long long)lo * d.is_o * d.elem_bytes;
+    d.out_base += (long long)lo * d.os_o;
+    d.On = len;
+    d.Ol = len;
+  }
+  return true;
 }
 
 JD_HD long long in_location(const PassDesc& d, int c, int t, int o, int b) {

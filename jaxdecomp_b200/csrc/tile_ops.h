@@ -10,8 +10,72 @@
 // columns per row are powers of two, so tile coordinates come from shifts.
 #pragma once
 #include "fft_core.h"
+#include "status.h"
+
+#ifndef JD_BOUNDS_CHECK
+#define JD_BOUNDS_CHECK 0
+#endif
 
 namespace jdb {
+
+// ---- checked stores -------------------------------------------------------------------------
+// Every store of a pass goes through store_elem / store_pair.  In a normal GPU build they are plain
+// stores.  The CPU emulation, and GPU builds compiled with -DJD_BOUNDS_CHECK=1 (the library variant
+// that JD_B200_BOUNDS=1 selects), first compare the destination with the size of the destination
+// buffer; a miss is recorded as JD_ERR_BOUNDS -- in the status block on the GPU, in a per-thread
+// record on the host -- and the access is skipped, so a wrong descriptor is reported instead of
+// corrupting a peer's memory.  (The reference relies on cuDecomp and XLA for its index arithmetic and
+// has no such mode.)
+struct BoundsMiss {
+  int32_t hit;
+  int32_t peer;
+  long long off, limit;
+};
+#if !defined(__CUDA_ARCH__)
+inline BoundsMiss& host_bounds_miss() {
+  static thread_local BoundsMiss m = {0, 0, 0, 0};
+  return m;
+}
+#endif
+
+JD_HD bool store_in_bounds(const PassDesc& d, int peer, long long off, int count) {
+#if JD_BOUNDS_CHECK || !defined(__CUDA_ARCH__)
+  if (d.out_limit <= 0) return true;
+  if (peer >= 0 && peer < d.npeers && off >= 0 && off + count <= d.out_limit) return true;
+#if defined(__CUDA_ARCH__)
+  StatusBlock* st = (StatusBlock*)d.status;
+  if (st != nullptr && atomicCAS(&st->code, 0, (int)JD_ERR_BOUNDS) == 0) {
+    st->peer = peer;
+    st->expected = (int32_t)(d.out_limit > 2147483647LL ? 2147483647LL : d.out_limit);
+    st->seen = (int32_t)(off > 2147483647LL ? 2147483647LL : (off < -2147483647LL ? -2147483647LL : off));
+    st->where = 200;
+    __threadfence_system();
+  }
+#else
+  BoundsMiss& m = host_bounds_miss();
+  if (!m.hit) m = BoundsMiss{1, peer, off, d.out_limit};
+#endif
+  return false;
+#else
+  return true;
+#endif
+}
+
+// True when a cross-rank wait failed earlier on this rank or on a peer (signal.cu sets the word): the
+// data in the exchange buffers is then incomplete, and every block of every later pass returns at once.
+JD_HD bool pass_aborted(const PassDesc& d) {
+#if defined(__CUDA_ARCH__)
+  return d.abort_word != nullptr && *(const volatile uint32_t*)d.abort_word != 0;
+#else
+  return d.abort_word != nullptr && *d.abort_word != 0;
+#endif
+}
+
+template <typename E>
+JD_HD void store_elem(const PassDesc& d, int peer, long long off, const E& v) {
+  if (!store_in_bounds(d, peer, off, 1)) return;
+  ((E*)d.out[peer])[off] = v;
+}
 
 template <typename E>
 struct elem_traits {
@@ -27,6 +91,12 @@ template <typename E>
 struct alignas(2 * sizeof(E)) pair_of {
   E a, b;
 };
+
+template <typename E>
+JD_HD void store_pair(const PassDesc& d, int peer, long long off, const pair_of<E>& v) {
+  if (!store_in_bounds(d, peer, off, 2)) return;
+  *(pair_of<E>*)((E*)d.out[peer] + off) = v;
+}
 
 template <typename E>
 JD_HD E zero_elem() {
@@ -174,11 +244,12 @@ JD_HD OutBase out_base_for(const PassDesc& d, int o, int b) {
   return r;
 }
 
-template <typename E>
-JD_HD E* out_ptr(const PassDesc& d, const OutBase& ob, int c, int t) {
+// peer and element offset of (c, t) given the (o, b) part
+JD_HD long long out_offset(const PassDesc& d, const OutBase& ob, int c, int t, int& peer) {
   const int pc = d.split_axis == 1 ? c / d.Cl : 0;
   const int pt = d.split_axis == 2 ? t / d.Tl : 0;
-  return (E*)d.out[ob.peer + pc + pt] + (ob.off + (long long)(c - pc * d.Cl) * d.os_c + (long long)(t - pt * d.Tl) * d.os_t);
+  peer = ob.peer + pc + pt;
+  return ob.off + (long long)(c - pc * d.Cl) * d.os_c + (long long)(t - pt * d.Tl) * d.os_t;
 }
 
 template <typename E>
@@ -205,15 +276,15 @@ JD_HD void tile_store(const PassDesc& d, const E* tile, int o, int t0, int c0, i
         int cl = c0 + c - pc * d.Cl;
         const E* src = tile + t * d.pitch;
         for (; c < cols; c += step) {
-          E* dst = (E*)d.out[ob.peer + pc + pt] + (toff + (long long)cl * d.os_c);
+          const long long doff = toff + (long long)cl * d.os_c;
           const int col = padidx(c, pad);
           if (vec) {
             pair_of<E> p;
             p.a = finish_value(d, src[col], c0 + c);
             p.b = finish_value(d, src[d.pitch + col], c0 + c);
-            *(pair_of<E>*)dst = p;
+            store_pair<E>(d, ob.peer + pc + pt, doff, p);
           } else {
-            *dst = finish_value(d, src[col], c0 + c);
+            store_elem<E>(d, ob.peer + pc + pt, doff, finish_value(d, src[col], c0 + c));
           }
           cl += step;
           if (d.split_axis == 1)
@@ -227,7 +298,9 @@ JD_HD void tile_store(const PassDesc& d, const E* tile, int o, int t0, int c0, i
       for (int e = tid; e < (cols << logT); e += nt) {
         const int c = e >> logT, t = e & (T - 1);
         if (t0 + t >= d.Tn) continue;
-        *out_ptr<E>(d, ob, c0 + c, t0 + t) = finish_value(d, tile[t * d.pitch + padidx(c, pad)], c0 + c);
+        int peer;
+        const long long doff = out_offset(d, ob, c0 + c, t0 + t, peer);
+        store_elem<E>(d, peer, doff, finish_value(d, tile[t * d.pitch + padidx(c, pad)], c0 + c));
       }
     }
   } else {
@@ -239,13 +312,17 @@ JD_HD void tile_store(const PassDesc& d, const E* tile, int o, int t0, int c0, i
         pair_of<E> p = *(const pair_of<E>*)(tile + t * d.pitch + padidx(c, pad));
         p.a = finish_value(d, p.a, c0 + c);
         p.b = finish_value(d, p.b, c0 + c + 1);
-        *(pair_of<E>*)out_ptr<E>(d, ob, c0 + c, t0 + t) = p;
+        int peer;
+        const long long doff = out_offset(d, ob, c0 + c, t0 + t, peer);
+        store_pair<E>(d, peer, doff, p);
       }
     } else {
       for (int e = tid; e < (T << logW); e += nt) {
         const int t = e >> logW, c = e & (W - 1);
         if (c >= cols || t0 + t >= d.Tn) continue;
-        *out_ptr<E>(d, ob, c0 + c, t0 + t) = finish_value(d, tile[t * d.pitch + padidx(c, pad)], c0 + c);
+        int peer;
+        const long long doff = out_offset(d, ob, c0 + c, t0 + t, peer);
+        store_elem<E>(d, peer, doff, finish_value(d, tile[t * d.pitch + padidx(c, pad)], c0 + c));
       }
     }
   }

@@ -8,6 +8,14 @@ stored beside it; the library is rebuilt only when the sources changed.  The
 reference builds its native module with CMake/scikit-build against cuDecomp
 (``CMakeLists.txt:1-123``); this build has no third-party dependency besides
 the CUDA toolkit and pybind11.
+
+Two variants of the library exist.  The normal one, and a checked one
+(``_jdb200_bounds``: same sources compiled with ``-DJD_BOUNDS_CHECK=1``) in
+which every store of every tile pass and halo kernel is compared with the size
+of its destination buffer first; a store that would leave the buffer is
+skipped and reported as ``BOUNDS`` through the status block.  Setting
+``JD_B200_BOUNDS=1`` before the package is imported selects the checked
+variant (several times slower; for debugging new plans and for the tests).
 """
 from __future__ import annotations
 
@@ -27,9 +35,16 @@ from .utils.errors import NativeExtensionError
 
 _HERE = Path(__file__).resolve().parent
 _CSRC = _HERE / "csrc"
-_SO = _HERE / ("_jdb200" + (sysconfig.get_config_var("EXT_SUFFIX") or ".so"))
-_HASH = _HERE / "_jdb200.hash"
-_OBJ = _CSRC / "build"
+_EXT = sysconfig.get_config_var("EXT_SUFFIX") or ".so"
+BOUNDS = os.environ.get("JD_B200_BOUNDS", "0") not in ("", "0")
+
+
+def _variant_paths(bounds: bool):
+    stem = "_jdb200_bounds" if bounds else "_jdb200"
+    return _HERE / (stem + _EXT), _HERE / (stem + ".hash"), _CSRC / ("build_bounds" if bounds else "build")
+
+
+_SO, _HASH, _OBJ = _variant_paths(BOUNDS)
 
 SOURCES = [
     "bindings.cpp",
@@ -78,27 +93,33 @@ def _source_hash() -> str:
     return h.hexdigest()
 
 
-def is_built() -> bool:
-    return _SO.exists() and _HASH.exists() and _HASH.read_text().strip() == _source_hash()
+def is_built(bounds: Optional[bool] = None) -> bool:
+    so, hsh, _ = _variant_paths(BOUNDS if bounds is None else bounds)
+    return so.exists() and hsh.exists() and hsh.read_text().strip() == _source_hash()
 
 
-def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False) -> Path:
-    """Compile every source for sm_100a and link ``_jdb200``.  Safe to call from
-    several processes at once (file lock); a no-op when the library is current."""
+def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False, bounds: Optional[bool] = None) -> Path:
+    """Compile every source for sm_100a and link ``_jdb200`` (or, with ``bounds=True``, the checked
+    variant ``_jdb200_bounds``; default: the variant this process uses).  Safe to call from several
+    processes at once (file lock); a no-op when the library is current."""
     nvcc = _nvcc()
     if nvcc is None:
         raise NativeExtensionError("nvcc not found; cannot build the native core")
+    bounds = BOUNDS if bounds is None else bool(bounds)
+    _SO, _HASH, _OBJ = _variant_paths(bounds)
     _OBJ.mkdir(parents=True, exist_ok=True)
     lock_path = _OBJ / ".lock"
     with open(lock_path, "w") as lock:
         fcntl.flock(lock, fcntl.LOCK_EX)
         try:
-            if is_built() and not force:
+            if is_built(bounds) and not force:
                 return _SO
             import pybind11
 
             inc = ["-I", sysconfig.get_paths()["include"], "-I", pybind11.get_include(), "-I", str(_CSRC)]
             flags = list(NVCC_FLAGS)
+            if bounds:
+                flags += ["-DJD_BOUNDS_CHECK=1"]
             if ptxas_info:
                 flags += ["-Xptxas", "-v"]
 
@@ -174,5 +195,6 @@ def so_path() -> Path:
 
 
 if __name__ == "__main__":
-    p = build(verbose=True, force="--force" in sys.argv, ptxas_info="--ptxas" in sys.argv)
+    p = build(verbose=True, force="--force" in sys.argv, ptxas_info="--ptxas" in sys.argv,
+              bounds=True if "--bounds" in sys.argv else None)
     print(p)

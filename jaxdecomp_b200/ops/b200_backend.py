@@ -25,14 +25,20 @@ import torch.distributed as dist
 from .. import native as _native
 from ..parallel.mesh import Mesh
 from ..utils.config import config
-from ..utils.errors import KernelStatusError, PeerTimeoutError, StaleEpochError
+from ..utils.errors import KernelStatusError, PeerAbortedError, PeerTimeoutError, StaleEpochError
 from . import passes as _passes
 from .plan import Step
 from .torch_backend import halo_regions
 
 _runtimes: Dict[tuple, "MeshRuntime"] = {}
+# bytes every new arena provides per slot at least (see utils.api.init / reserve_workspace)
+_default_slot_bytes = 0
 # switches that change how a plan is tiled: part of the plan key
-_TUNING_ENV = ("JD_B200_TILE_T", "JD_B200_BULK", "JD_B200_INTRAPAD", "JD_B200_ROWPAD", "JD_B200_FAST")
+_TUNING_ENV = ("JD_B200_TILE_T", "JD_B200_BULK", "JD_B200_INTRAPAD", "JD_B200_ROWPAD", "JD_B200_FAST",
+               "JD_B200_PIPE_MIN_BYTES")
+# exchange passes smaller than this (bytes per rank) are not pipelined: below it the extra launches and
+# per-chunk barriers cost more than the overlap gains
+_PIPE_MIN_BYTES = 256 << 20
 
 
 def _stream() -> int:
@@ -60,12 +66,19 @@ class MeshRuntime:
         self._shapes: Dict[int, tuple] = {}
         self._pycache: Dict[tuple, tuple] = {}
         self.plan_hits = 0
+        self.arena_generation = 0  # how many times the arena was (re)created
 
     # ---- arena --------------------------------------------------------------------------------
     def ensure_arena(self, slot_bytes: int) -> None:
-        """Collective: every rank of the mesh must call this with the same size."""
+        """Collective: every rank of the mesh must call this with the same size.
+
+        Growing the arena stops the world (device synchronise, close all peer mappings, host barrier,
+        allocate, exchange handles, reopen), so it should happen once: size the workspace up front with
+        ``init(workspace_bytes=...)`` or ``reserve_workspace`` when the largest problem is known."""
         if self.rt.has_arena() and self.rt.slot_bytes() >= slot_bytes:
             return
+        slot_bytes = max(int(slot_bytes), int(_default_slot_bytes))
+        self.arena_generation += 1
         torch.cuda.synchronize()
         if self.world > 1:
             if self.rt.has_arena():
@@ -82,10 +95,14 @@ class MeshRuntime:
         if not self.rt.has_arena():
             return
         torch.cuda.synchronize()
+        met = False
         if self.world > 1 and collective and dist.is_initialized():
             self.rt.close_peers()
             dist.barrier(group=self.group)
-        self.rt.destroy_arena()
+            met = True
+        # Without the host barrier a peer may still have this rank's blocks mapped and be writing to
+        # them: only the imports are closed then, and the exported blocks stay until the process ends.
+        self.rt.destroy_arena(met or self.world == 1)
 
     # ---- status ---------------------------------------------------------------------------------
     def check_status(self, sync: bool = False) -> None:
@@ -102,6 +119,8 @@ class MeshRuntime:
             raise PeerTimeoutError(msg, peer=peer, expected=expected, seen=seen)
         if name == "STALE_EPOCH":
             raise StaleEpochError(msg)
+        if name == "PEER_ABORTED":
+            raise PeerAbortedError(msg, peer=peer)
         raise KernelStatusError(msg)
 
     # ---- plans -----------------------------------------------------------------------------------
@@ -148,6 +167,15 @@ class MeshRuntime:
             st.desc = d
             plan_steps.append(st)
             cur_kind = out_kind
+        # pipelined transports: overlap every exchange pass with the local pass that consumes it
+        min_bytes = int(os.environ.get("JD_B200_PIPE_MIN_BYTES", _PIPE_MIN_BYTES))
+        if config.pipelined and config.pipeline_chunks >= 2 and bytes_per >= min_bytes:
+            for i in range(n - 1):
+                cut = _passes.pipeline_cut(specs[i], specs[i + 1], int(config.pipeline_chunks))
+                if cut is None or plan_steps[i].out_kind == nat.BUF_USER_OUT:
+                    continue
+                plan_steps[i].pipe_role, plan_steps[i + 1].pipe_role, plan_steps[i].pipe_chunks = cut
+                plan_steps[i].pipe_grid_limit = int(config.pipeline_ctas)
         if cur_kind != nat.BUF_USER_OUT:
             st = nat.PlanStep()
             st.in_kind = cur_kind
@@ -166,7 +194,7 @@ class MeshRuntime:
         nbatch = x.shape[0] if nb else 1
         lshape = tuple(x.shape[nb:])
         env = tuple(os.environ.get(k, "") for k in _TUNING_ENV)
-        pykey = (tuple(steps), lshape, x.dtype, bool(inverse), float(scale), nbatch, env)
+        pykey = (tuple(steps), lshape, x.dtype, bool(inverse), float(scale), nbatch, env, config.snapshot())
         hit = self._pycache.get(pykey)
         if hit is None:
             if not _passes._group_steps(steps, self.mesh.pdims):
@@ -262,6 +290,11 @@ class MeshRuntime:
         is_f64 = int(g.dtype in (torch.float64, torch.complex128))
         self.rt.halo(pack, unpack, zero, S0, S1, S2, B, eb, is_f64, 1, g.data_ptr(), out.data_ptr(), _stream())
         return out
+
+
+def set_default_workspace(slot_bytes: int) -> None:
+    global _default_slot_bytes
+    _default_slot_bytes = max(0, int(slot_bytes))
 
 
 def get_runtime(mesh: Mesh) -> MeshRuntime:

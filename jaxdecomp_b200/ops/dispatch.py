@@ -12,6 +12,7 @@ import torch
 from ..utils.config import (
     HALO_COMM_P2P,
     TRANSPOSE_COMM_P2P,
+    TRANSPOSE_COMM_P2P_PL,
     canonical_backend,
     config,
 )
@@ -25,8 +26,8 @@ def resolve_backend(backend: str, x: torch.Tensor, family: str = "transpose") ->
     if b == "auto":
         if x.is_cuda:
             comm = config.halo_comm_backend if family == "halo" else config.transpose_comm_backend
-            native = HALO_COMM_P2P if family == "halo" else TRANSPOSE_COMM_P2P
-            b = "b200" if comm == native else "torch"
+            native = (HALO_COMM_P2P,) if family == "halo" else (TRANSPOSE_COMM_P2P, TRANSPOSE_COMM_P2P_PL)
+            b = "b200" if comm in native else "torch"
         else:
             b = "torch"
     if b == "b200":

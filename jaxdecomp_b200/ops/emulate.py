@@ -41,9 +41,16 @@ def split_blocks(x: torch.Tensor, pdims: Sequence[int], spec_axes=(0, 1)) -> Lis
 
 
 def emulate_steps(blocks: List[torch.Tensor], steps: Sequence[Step], pdims: Sequence[int], inverse: bool = False,
-                  scale: float = 1.0) -> List[torch.Tensor]:
+                  scale: float = 1.0, pipeline_chunks: int = 0) -> List[torch.Tensor]:
     """Run a step list on the blocks of all ranks (row-major rank order) and
-    return the per-rank results."""
+    return the per-rank results.
+
+    With ``pipeline_chunks >= 2`` every exchange pass that the native backend
+    would pipeline with the local pass after it (:func:`passes.pipeline_cut`)
+    is executed the way the pipelined executor does: chunk by chunk, the
+    consumer's chunk k right after chunk k of all producers and *before* their
+    chunk k+1 exists -- so a consumer chunk that read outside its producers'
+    chunk would see zeros and the result would differ."""
     from .. import native as _native
 
     nat = _native.require()
@@ -63,25 +70,51 @@ def emulate_steps(blocks: List[torch.Tensor], steps: Sequence[Step], pdims: Sequ
     npass = len(compiled[0])
     last_fft = max((i for i, p in enumerate(compiled[0]) if p.fft), default=-1)
     cur = [b.contiguous() for b in blocks]
-    for i in range(npass):
-        shape_i = compiled[0][i].out_shape
-        full = ((nbatch,) if blocks[0].dim() == 4 else ()) + tuple(shape_i)
-        nxt = [torch.zeros(full, dtype=dtype) for _ in range(world)]
-        for r in range(world):
-            sp = compiled[r][i]
-            coords = (r // p1, r % p1)
-            d = _passes.fill_desc(nat, sp, eb, inverse, scale if i == last_fft else 1.0, nbatch,
-                                  remote=sp.npeers > 1, device_tables=False)
-            d.use_bulk = 0
-            d.in_ptr = cur[r].data_ptr()
-            for p in range(sp.npeers):
-                if sp.mesh_axis is None:
-                    dst = r
-                elif sp.mesh_axis == 0:
-                    dst = p * p1 + coords[1]
-                else:
-                    dst = coords[0] * p1 + p
-                d.set_out(p, nxt[dst].data_ptr())
-            nat.run_pass_host(d)
+
+    def alloc(i):
+        full = ((nbatch,) if blocks[0].dim() == 4 else ()) + tuple(compiled[0][i].out_shape)
+        return [torch.zeros(full, dtype=dtype) for _ in range(world)]
+
+    def desc(i, r, src, dst_bufs):
+        sp = compiled[r][i]
+        coords = (r // p1, r % p1)
+        d = _passes.fill_desc(nat, sp, eb, inverse, scale if i == last_fft else 1.0, nbatch,
+                              remote=sp.npeers > 1, device_tables=False)
+        d.use_bulk = 0
+        d.in_ptr = src[r].data_ptr()
+        for p in range(sp.npeers):
+            if sp.mesh_axis is None:
+                dst = r
+            elif sp.mesh_axis == 0:
+                dst = p * p1 + coords[1]
+            else:
+                dst = coords[0] * p1 + p
+            d.set_out(p, dst_bufs[dst].data_ptr())
+        return d
+
+    i = 0
+    while i < npass:
+        cut = None
+        if pipeline_chunks >= 2 and i + 1 < npass:
+            cut = _passes.pipeline_cut(compiled[0][i], compiled[0][i + 1], pipeline_chunks)
+        if cut is None:
+            nxt = alloc(i)
+            for r in range(world):
+                nat.run_pass_host(desc(i, r, cur, nxt))
+            cur = nxt
+            i += 1
+            continue
+        prole, crole, K = cut
+        mid, nxt = alloc(i), alloc(i + 1)
+        pd = [desc(i, r, cur, mid) for r in range(world)]
+        cd = [desc(i + 1, r, mid, nxt) for r in range(world)]
+        ext = compiled[0][i].ext[prole - 1]
+        step = ext // K
+        for k in range(K):
+            for r in range(world):
+                nat.run_pass_host(pd[r].restricted(prole, k * step, step))
+            for r in range(world):
+                nat.run_pass_host(cd[r].restricted(crole, k * step, step))
         cur = nxt
+        i += 2
     return cur

@@ -48,14 +48,17 @@ def _str_to_fft_type(s: str) -> str:
     raise ValueError(f"Unrecognized string for FFT type: {s}")
 
 
-def _run(x: torch.Tensor, mesh, steps, inverse: bool, scale: float, backend: str) -> torch.Tensor:
+def _run(x: torch.Tensor, mesh, steps, inverse: bool, scale: float, backend: str, contiguous: bool = True) -> torch.Tensor:
     if backend == "b200":
         from . import b200_backend
 
         return b200_backend.run_steps(x, steps, mesh, inverse, scale)
     from . import torch_backend
 
-    y = torch_backend.run_steps(x, steps, mesh, inverse)
+    if mesh.pdims[0] * mesh.pdims[1] == 1:
+        y = torch_backend.fft_single_device(x, inverse, contiguous)
+    else:
+        y = torch_backend.run_steps(x, steps, mesh, inverse)
     if scale != 1.0:
         y = y * scale
     return y
@@ -68,7 +71,7 @@ class _DistFFT(torch.autograd.Function):
     def forward(ctx, x, mesh, inverse, contiguous, scale, backend, pencil_type):
         ctx.args = (mesh, inverse, contiguous, scale, backend, pencil_type)
         steps = _plan.fft_steps(pencil_type, inverse, contiguous, native=(backend == "b200"))
-        return _run(x, mesh, steps, inverse, scale, backend)
+        return _run(x, mesh, steps, inverse, scale, backend, contiguous)
 
     @staticmethod
     def backward(ctx, g):

@@ -56,6 +56,7 @@ class PassSpec:
     fft: bool
     mesh_axis: Optional[int]            # decomposition axis of the all-to-all, if any
     plain: bool = False                 # same strides in and out, single destination: may run in place
+    concat_role: Optional[int] = None   # role (0 c, 1 t, 2 o) of the axis the all-to-all concatenates along
 
     @property
     def numel(self) -> int:
@@ -162,9 +163,49 @@ def compile_passes(steps: Sequence[Step], local_shape: Sequence[int], pdims: Seq
             out_base=out_base, npeers=P, fft=g.fft_axis is not None, mesh_axis=maxis,
         )
         spec.plain = P == 1 and tuple(spec.in_strides) == tuple(spec.out_strides)
+        if g.a2a is not None:
+            spec.concat_role = roles.index(concat)
         passes.append(spec)
         shape = F
     return passes, tuple(shape)
+
+
+# ---- pipelining of an exchange pass with the local pass that consumes it -------------------------------------
+
+def pipeline_cut(prod: PassSpec, cons: PassSpec, want_chunks: int) -> Optional[Tuple[int, int, int]]:
+    """How to cut an exchange pass and the local pass after it into matching chunks.
+
+    Returns ``(producer role, consumer role, chunks)`` with roles numbered as in the native
+    descriptor (2 = t, 3 = o), or ``None`` when the pair cannot be pipelined.  The cut runs along an
+    axis of the exchanged array that
+
+    * is neither the producer's transform/split axis nor the axis its all-to-all concatenates along
+      (every source rank then contributes to every chunk, and chunk k of all sources together is
+      exactly the part of the array with that axis in chunk k),
+    * is not the consumer's transform axis (the consumer needs whole rows of that one),
+
+    so that chunk k of the consumer reads only what chunk k of the producers wrote.  The chunk count
+    is the largest ``want_chunks / 2**i >= 2`` that divides the extent into whole tiles (ranges along a
+    ``t`` axis must be multiples of 32 rows, the largest tile height).
+    """
+    if prod.npeers <= 1 or cons.npeers != 1 or tuple(prod.out_shape) != tuple(cons.in_shape) or want_chunks < 2:
+        return None
+    for pr in (2, 1):
+        if prod.chunks[pr] != prod.ext[pr] or prod.concat_role == pr or prod.ext[pr] < 2:
+            continue
+        for cr in (2, 1):
+            if cons.in_strides[cr] != prod.out_strides[pr] or cons.ext[cr] != prod.ext[pr]:
+                continue
+            ext = prod.ext[pr]
+            k = int(want_chunks)
+            while k >= 2:
+                ok = ext % k == 0
+                if ok and (pr == 1 or cr == 1):
+                    ok = (ext // k) % 32 == 0
+                if ok:
+                    return pr + 1, cr + 1, k
+                k //= 2
+    return None
 
 
 # ---- dtype-dependent tiling ----------------------------------------------------------------------------------
@@ -332,6 +373,7 @@ def fill_desc(native, spec: PassSpec, elem_bytes: int, inverse: bool, scale: flo
     d.os_b = spec.numel
     d.Cl, d.Tl, d.Ol = spec.chunks
     d.out_base = spec.out_base
+    d.out_limit = spec.numel * int(batch)
     d.npeers = spec.npeers
     d.elem_bytes = elem_bytes
     d.inverse = int(bool(inverse)) if spec.fft else 0

@@ -44,6 +44,21 @@ def run_steps(x: torch.Tensor, steps: Sequence[Step], mesh: Mesh, inverse: bool)
     return x
 
 
+def fft_single_device(x: torch.Tensor, inverse: bool, contiguous: bool) -> torch.Tensor:
+    """The transform on a mesh of one rank, the way the reference does it there: one ``fftn`` over the
+    three axes plus, in contiguous mode, one axis rotation (``src/jaxdecomp/_src/jax/fft.py:285-288``) --
+    not three 1-D transforms with a copy after each.  Un-normalised in both directions."""
+    nb = x.dim() - 3
+    dims = (nb, nb + 1, nb + 2)
+    lead = tuple(range(nb))
+    if not inverse:
+        y = torch.fft.fftn(x, dim=dims)
+        return y.permute(lead + (nb + 1, nb + 2, nb)).contiguous() if contiguous else y
+    if contiguous:
+        x = x.permute(lead + (nb + 2, nb, nb + 1))
+    return torch.fft.ifftn(x, dim=dims, norm="forward").contiguous()
+
+
 def halo_exchange(x: torch.Tensor, halo_extents, halo_periods, mesh: Mesh) -> torch.Tensor:
     """Ghost-cell exchange on the two sharded axes of an already padded block.
 

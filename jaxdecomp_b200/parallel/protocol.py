@@ -7,7 +7,10 @@ slots hold a value ``>= e`` in wrap-around arithmetic.  A wait that runs out of
 budget returns ``TIMEOUT_PEER_SIGNAL`` with the peer, the expected and the
 observed epoch; a slot that is *ahead* of the expected epoch by more than one
 barrier is reported as ``STALE_EPOCH`` (a rank replayed or skipped barriers).
-The model lets fault scenarios -- a withheld signal, a corrupted epoch -- be
+A rank whose wait failed sets the abort word of every rank; an aborted rank
+signals nothing more and its barriers return ``PEER_ABORTED``, as do the
+kernels' (``csrc/signal.cu``).  ``PipelineModel`` runs the per-chunk barriers
+of the pipelined transports on top of it.  The model lets fault scenarios -- a withheld signal, a corrupted epoch -- be
 tested on CPU ranks without ever making a GPU wait on something that cannot
 arrive.  The reference has no failure detection: a dead peer blocks its NCCL or
 MPI collective forever (``src/csrc/include/checks.h:29-72``).
@@ -30,6 +33,7 @@ from ..utils.errors import DecompError
 OK = 0
 TIMEOUT_PEER_SIGNAL = -3
 STALE_EPOCH = -4
+PEER_ABORTED = -8
 _MASK = 0xFFFFFFFF
 
 
@@ -54,6 +58,7 @@ class FlagBoard:
         self.n = n
         self.slots: List[List[int]] = [[0] * n for _ in range(n)]
         self.counter = [0] * n
+        self.aborted = [0] * n  # abort word of every rank: 0, or 1 + the rank whose wait failed
         self.drop = drop  # drop(src, dst, epoch) -> True withholds that signal
 
     def signal(self, src: int, epoch: int) -> None:
@@ -78,13 +83,59 @@ class FlagBoard:
         return WaitResult(TIMEOUT_PEER_SIGNAL, pending[0], epoch & _MASK, pending[1])
 
     def barrier_all(self, polls: int = 8) -> List[WaitResult]:
-        """One barrier round executed by every rank: all signal, then all wait."""
+        """One barrier round executed by every rank: all signal, then all wait.  An aborted rank
+        counts the barrier but neither signals nor waits; a rank whose wait fails aborts everyone."""
         epochs = []
         for r in range(self.n):
             self.counter[r] = (self.counter[r] + 1) & _MASK
             epochs.append(self.counter[r])
-            self.signal(r, self.counter[r])
-        return [self.wait(r, epochs[r], polls) for r in range(self.n)]
+            if not self.aborted[r]:
+                self.signal(r, self.counter[r])
+        out, failed = [], []
+        for r in range(self.n):
+            if self.aborted[r]:
+                out.append(WaitResult(PEER_ABORTED, self.aborted[r] - 1, epochs[r]))
+                continue
+            w = self.wait(r, epochs[r], polls)
+            if w.code != OK:
+                failed.append(r)
+            out.append(w)
+        # a wait fails only after its whole budget, by which time the healthy ranks have left this
+        # barrier: they see the abort word in their next one
+        for r in failed:
+            for q in range(self.n):
+                if not self.aborted[q]:
+                    self.aborted[q] = r + 1
+        return out
+
+
+class PipelineModel:
+    """Per-chunk barriers of a pipelined exchange (``csrc/runtime.cpp``, ``run_pipelined``).
+
+    Every rank issues its exchange chunks in order; before the local pass may work on chunk ``k`` the
+    rank runs one barrier, which it can only signal once its own chunk ``k`` has been issued and which
+    completes once every rank has signalled.  ``run`` plays the chunks of all ranks in lock step and
+    returns ``(rank, chunk, code)`` for every barrier; ``consumed_before_produced`` counts local
+    passes that started on a chunk some rank had not produced yet (must stay 0)."""
+
+    def __init__(self, board: FlagBoard, chunks: int):
+        self.board, self.chunks = board, chunks
+        self.consumed_before_produced = 0
+
+    def run(self, polls: int = 8):
+        n = self.board.n
+        produced = [[False] * self.chunks for _ in range(n)]
+        log = []
+        for k in range(self.chunks):
+            for r in range(n):
+                if not self.board.aborted[r]:
+                    produced[r][k] = True  # exchange chunk k of rank r: stores into every peer
+            res = self.board.barrier_all(polls)
+            for r in range(n):
+                log.append((r, k, res[r].code))
+                if res[r].code == OK and not all(produced[q][k] for q in range(n)):
+                    self.consumed_before_produced += 1
+        return log
 
 
 class PeerDeadError(DecompError):
@@ -131,9 +182,15 @@ class HealthMonitor:
         now = time.time()
         out = []
         for r in range(self.world):
+            key = f"hb/{r}"
             try:
-                out.append(now - float(self.store.get(f"hb/{r}").decode()))
-            except Exception:  # noqa: BLE001 - key not written yet
+                # get() on a key that was never written blocks for the store's own time-out (minutes):
+                # ask first whether the key exists, and treat a missing key as "never seen"
+                if not self.store.check([key]):
+                    out.append(float("inf"))
+                    continue
+                out.append(now - float(self.store.get(key).decode()))
+            except Exception:  # noqa: BLE001 - the store is gone
                 out.append(float("inf"))
         return out
 

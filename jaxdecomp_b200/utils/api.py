@@ -46,15 +46,32 @@ def make_config(gdims=(0, 0, 0), pdims=(1, 1), transpose_comm_backend=TRANSPOSE_
 _initialised = False
 
 
-def init() -> None:
+def init(workspace_bytes: Optional[int] = None) -> None:
     """Load the native core eagerly on machines with a GPU.  Optional: every op
-    initialises what it needs on first use."""
+    initialises what it needs on first use.
+
+    ``workspace_bytes`` pre-sizes the peer-visible workspace: every arena created afterwards holds
+    at least that many bytes per exchange buffer (there are two), so that no later, larger problem
+    makes it grow -- growth is a stop-the-world collective.  A good value is the size of the largest
+    local block that will be transformed (``get_fft_workspace_size`` reports it for a grid)."""
     global _initialised
     if torch.cuda.is_available():
         from .. import native
 
         native.require()
+    if workspace_bytes is not None:
+        from ..ops import b200_backend
+
+        b200_backend.set_default_workspace(int(workspace_bytes))
     _initialised = True
+
+
+def reserve_workspace(mesh, slot_bytes: int) -> None:
+    """Create (or grow) the peer-visible workspace of ``mesh`` now, with ``slot_bytes`` per exchange
+    buffer.  Collective over the ranks of the mesh's decomposition group; CUDA only."""
+    from ..ops import b200_backend
+
+    b200_backend.get_runtime(mesh).ensure_arena(int(slot_bytes))
 
 
 def finalize() -> None:

@@ -35,7 +35,10 @@ class TransposeCommBackend(enum.IntEnum):
     TRANSPOSE_COMM_NCCL_PL = 5
     TRANSPOSE_COMM_NVSHMEM = 6
     TRANSPOSE_COMM_NVSHMEM_PL = 7
+    # transports native to this package: fused peer-store kernels, each exchange pass followed by its
+    # barrier (P2P) or cut into chunks that overlap with the local pass that consumes them (P2P_PL)
     TRANSPOSE_COMM_P2P = 16
+    TRANSPOSE_COMM_P2P_PL = 17
 
 
 class TransposeType(enum.IntEnum):
@@ -68,6 +71,7 @@ TRANSPOSE_COMM_NCCL_PL = TransposeCommBackend.TRANSPOSE_COMM_NCCL_PL
 TRANSPOSE_COMM_NVSHMEM = TransposeCommBackend.TRANSPOSE_COMM_NVSHMEM
 TRANSPOSE_COMM_NVSHMEM_PL = TransposeCommBackend.TRANSPOSE_COMM_NVSHMEM_PL
 TRANSPOSE_COMM_P2P = TransposeCommBackend.TRANSPOSE_COMM_P2P
+TRANSPOSE_COMM_P2P_PL = TransposeCommBackend.TRANSPOSE_COMM_P2P_PL
 TRANSPOSE_XY = TransposeType.TRANSPOSE_XY
 TRANSPOSE_YZ = TransposeType.TRANSPOSE_YZ
 TRANSPOSE_ZY = TransposeType.TRANSPOSE_ZY
@@ -103,19 +107,25 @@ class DecompConfig:
     """Mutable configuration state.
 
     ``halo_comm_backend`` / ``transpose_comm_backend`` keep the reference's
-    field names; the NCCL values select the all_to_all / send-recv baseline
-    backend and the P2P values select the fused peer-store kernels when the
-    per-call ``backend`` argument is ``'auto'``.
+    field names.  With the per-call ``backend`` argument at ``'auto'``, the
+    NCCL/MPI/NVSHMEM values select the all_to_all / send-recv baseline backend
+    and the P2P values the fused peer-store kernels.  As in the reference
+    (``src/csrc/include/jaxdecomp.h:13-18``) the ``*_PL`` transposes are the
+    pipelined ones: on the native backend every exchange pass that is followed
+    by a local pass is cut into ``pipeline_chunks`` chunks, and the local pass
+    works on chunk k while chunk k+1 crosses NVLink.  ``pipeline_ctas`` limits
+    the thread blocks of an exchange chunk (0: no limit) so that the local pass
+    finds free SMs.
     """
 
     halo_comm_backend: HaloCommBackend = HALO_COMM_P2P
-    transpose_comm_backend: TransposeCommBackend = TRANSPOSE_COMM_P2P
+    transpose_comm_backend: TransposeCommBackend = TRANSPOSE_COMM_P2P_PL
     transpose_axis_contiguous: bool = True
     backend: str = "auto"
-    wait_timeout_ms: int = int(os.environ.get("JD_B200_WAIT_TIMEOUT_MS", "2000"))
-    deterministic_accumulate: bool = True
+    wait_timeout_ms: int = int(os.environ.get("JD_B200_WAIT_TIMEOUT_MS", "10000"))
     reference_compat_halo_grad: bool = False
-    trace: bool = False
+    pipeline_chunks: int = int(os.environ.get("JD_B200_PIPE_CHUNKS", "4"))
+    pipeline_ctas: int = int(os.environ.get("JD_B200_PIPE_CTAS", "0"))
 
     def update(self, key, value):
         names = {f.name for f in fields(self)}
@@ -123,10 +133,24 @@ class DecompConfig:
             raise ValueError(f"key {key} is not a valid configuration key")
         if key == "backend":
             value = canonical_backend(value)
+        elif key == "transpose_comm_backend":
+            value = TransposeCommBackend(int(value))
+        elif key == "halo_comm_backend":
+            value = HaloCommBackend(int(value))
+        elif key in ("pipeline_chunks", "pipeline_ctas", "wait_timeout_ms"):
+            value = int(value)
+            if value < 0:
+                raise ValueError(f"{key} must not be negative")
         setattr(self, key, value)
 
+    @property
+    def pipelined(self) -> bool:
+        """True when the configured transpose transport is one of the pipelined (``*_PL``) ones."""
+        return TransposeCommBackend(int(self.transpose_comm_backend)).name.endswith("_PL")
+
     def snapshot(self) -> tuple:
-        """Hashable view used as part of plan-cache keys."""
+        """Hashable view of every field; the native backend puts it into its plan-cache keys, so a plan
+        built under one configuration is never reused under another."""
         return tuple(getattr(self, f.name) for f in fields(self))
 
 

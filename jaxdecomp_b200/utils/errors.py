@@ -37,7 +37,18 @@ class PeerTimeoutError(DecompError):
 
 
 class StaleEpochError(DecompError):
-    """A signal carried an epoch older than the one the protocol expects."""
+    """A peer's signal was more than one barrier ahead of the barrier this rank was waiting in: the
+    ranks no longer count the same barriers (a replayed or skipped barrier, a corrupted flag)."""
+
+
+class PeerAbortedError(DecompError):
+    """Another rank's bounded wait failed and it marked the whole group as aborted; the exchange
+    buffers hold incomplete data, every later kernel of this rank returned without computing, and the
+    arena must be re-created (``finalize()`` then the next call) before the mesh is used again."""
+
+    def __init__(self, message: str, peer: int = -1):
+        super().__init__(message)
+        self.peer = peer
 
 
 class KernelStatusError(DecompError):

@@ -25,41 +25,72 @@ def _rel(a, b):
     return ((a - b).abs().max() / d).item()
 
 
+def _fft_case(x, mesh, tol, tag):
+    """Forward against the baseline backend on the same ranks, inverse back to the input, and the
+    pipelined transport bit-identical to the plain one."""
+    k_ref = jd.pfft3d(x, backend="torch")
+    jd.config.update("transpose_comm_backend", jd.TRANSPOSE_COMM_P2P)
+    k0 = jd.pfft3d(x, backend="b200")
+    b0 = jd.pifft3d(k0, backend="b200")
+    jd.config.update("transpose_comm_backend", jd.TRANSPOSE_COMM_P2P_PL)
+    k = jd.pfft3d(x, backend="b200")
+    b = jd.pifft3d(k, backend="b200")
+    assert tuple(k.spec) == tuple(k_ref.spec) and k.local.shape == k_ref.local.shape, tag
+    assert _rel(k.local, k_ref.local) < tol, tag
+    assert _rel(b.local, x.local) < 10 * tol, tag
+    assert torch.equal(k.local, k0.local) and torch.equal(b.local, b0.local), tag
+
+
+def _transposes_case(x, mesh, pencil):
+    y = jd.transposeXtoY(x, backend="b200")
+    assert torch.equal(y.local, jd.transposeXtoY(x, backend="torch").local)
+    z = jd.transposeYtoZ(y, backend="b200")
+    assert torch.equal(z.local, jd.transposeYtoZ(y, backend="torch").local)
+    y2 = jd.transposeZtoY(z, backend="b200")
+    assert torch.equal(y2.local, y.local)
+    assert torch.equal(jd.transposeYtoX(y2, backend="b200").local, x.local)
+    if pencil:
+        zz = jd.transposeXtoZ(x, backend="b200")
+        assert torch.equal(zz.local, jd.transposeXtoZ(x, backend="torch").local)
+        assert torch.equal(jd.transposeZtoX(zz, backend="b200").local, x.local)
+
+
 def _ops_worker(rank, world):
+    from jaxdecomp_b200.ops import b200_backend
+
     dev = torch.device("cuda", rank)
     for pdims in _pdims_list(world):
         mesh = jd.make_mesh(pdims, ("z", "y"))
         p0, p1 = pdims
+        rt = b200_backend.get_runtime(mesh)
+        # one arena for everything this mesh will run (the largest block below is 256x512x1024 complex64)
+        jd.reserve_workspace(mesh, 256 * 512 * 1024 * 8 // world)
+        grew = rt.arena_generation
         for contiguous in (True, False):
             jd.config.update("transpose_axis_contiguous", contiguous)
-            # largest block first: the peer-visible arena then grows once per mesh
-            for dtype, shape, tol in ((torch.complex64, (96, 192, 160), 3e-6), (torch.complex64, (64, 32, 128), 3e-6),
-                                      (torch.complex128, (24, 40, 56), 1e-12)):
-                g = torch.Generator(device="cpu").manual_seed(1234)
-                xg = torch.randn(shape, generator=g, dtype=torch.float64).to(dtype)
-                x = jd.shard(xg.to(dev), mesh)
-                k_ref = jd.pfft3d(x, backend="torch")
-                k = jd.pfft3d(x, backend="b200")
-                assert tuple(k.spec) == tuple(k_ref.spec) and k.local.shape == k_ref.local.shape
-                assert _rel(k.local, k_ref.local) < tol, (pdims, contiguous, dtype)
-                b = jd.pifft3d(k, backend="b200")
-                assert _rel(b.local, x.local) < 10 * tol, (pdims, contiguous, dtype)
+            cases = [(torch.complex64, (64, 32, 128), 3e-6), (torch.complex128, (24, 40, 56), 1e-12)]
+            if contiguous:
+                # the sizes of the headline run: 1024-point rows, the large tiles of the exchange pass
+                cases = [(torch.complex64, (256, 512, 1024), 3e-6), (torch.complex128, (128, 256, 512), 1e-12),
+                         (torch.complex64, (96, 192, 160), 3e-6)] + cases
+            for dtype, shape, tol in cases:
+                g = torch.Generator(device=dev).manual_seed(1234)
+                real = torch.float32 if dtype == torch.complex64 else torch.float64
+                xg = torch.complex(torch.randn(shape, generator=g, device=dev, dtype=real),
+                                   torch.randn(shape, generator=g, device=dev, dtype=real))
+                x = jd.shard(xg, mesh)
+                del xg
+                _fft_case(x, mesh, tol, (pdims, contiguous, dtype, shape))
+                if contiguous and shape[2] == 1024:
+                    _transposes_case(x, mesh, p0 > 1 and p1 > 1)
+                del x
             # transposes, exact
             for dtype in (torch.float32, torch.complex128):
                 xg = torch.randn((16, 32, 64), generator=torch.Generator().manual_seed(7), dtype=torch.float64).to(dtype)
-                x = jd.shard(xg.to(dev), mesh)
-                y = jd.transposeXtoY(x, backend="b200")
-                assert torch.equal(y.local, jd.transposeXtoY(x, backend="torch").local)
-                z = jd.transposeYtoZ(y, backend="b200")
-                assert torch.equal(z.local, jd.transposeYtoZ(y, backend="torch").local)
-                y2 = jd.transposeZtoY(z, backend="b200")
-                assert torch.equal(y2.local, y.local)
-                assert torch.equal(jd.transposeYtoX(y2, backend="b200").local, x.local)
-                if p0 > 1 and p1 > 1:
-                    zz = jd.transposeXtoZ(x, backend="b200")
-                    assert torch.equal(zz.local, jd.transposeXtoZ(x, backend="torch").local)
-                    assert torch.equal(jd.transposeZtoX(zz, backend="b200").local, x.local)
+                _transposes_case(jd.shard(xg.to(dev), mesh), mesh, p0 > 1 and p1 > 1)
         jd.config.update("transpose_axis_contiguous", True)
+        assert rt.rt.pipelined_sections() > 0
+        assert rt.arena_generation == grew, "the reserved workspace should have covered every case"
         # halos: copy and accumulate, periodic and not
         for periods in ((True, True), (False, True)):
             for dtype in (torch.float32, torch.float64):
@@ -81,10 +112,11 @@ def _ops_worker(rank, world):
         kr = jd.pfft3d(jd.ShardedTensor(xr, mesh), backend="torch")
         (kr.local.abs() ** 2 * (rank + 1)).sum().backward()
         assert _rel(xl.grad, xr.grad) < 1e-5
-        from jaxdecomp_b200.ops import b200_backend
-
         b200_backend.check_status(mesh, sync=True)
         jd.finalize()
+
+
+_ENV = {"NCCL_NVLS_ENABLE": "0", "JD_B200_PIPE_MIN_BYTES": "0"}
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs at least two GPUs")
@@ -92,7 +124,7 @@ def test_native_ops_match_baseline_on_all_gpus():
     world = 1
     while world * 2 <= min(_ngpu(), 8):
         world *= 2
-    run_ranks(_ops_worker, world, backend="nccl", env={"NCCL_NVLS_ENABLE": "0"}, timeout=900)
+    run_ranks(_ops_worker, world, backend="nccl", env=_ENV, timeout=900)
 
 
 def _lpt_worker(rank, world):

@@ -147,6 +147,72 @@ def test_bounded_wait_times_out_with_status_and_context_survives():
     assert issubclass(PeerTimeoutError, RuntimeError)
 
 
+def test_wait_reports_a_slot_that_is_too_far_ahead_as_stale():
+    """A slot more than one barrier ahead of the awaited epoch means the ranks stopped counting the
+    same barriers; the wait returns at once with STALE_EPOCH (nothing waits, nothing faults)."""
+    from jaxdecomp_b200 import native
+
+    nat = native.require()
+    rt = nat.Runtime(1, 0)
+    rt.create_arena(1 << 20)
+    rt.poke_flag(0, 40)  # this rank's own slot jumps to epoch 40
+    stream = torch.cuda.current_stream().cuda_stream
+    rt.wait_only(1, 7, 50, stream)
+    torch.cuda.synchronize()
+    code, peer, expected, seen, where = rt.read_status()
+    assert nat.status_name(code) == "STALE_EPOCH" and peer == 0 and expected == 7 and seen == 40
+    rt.clear_status()
+    rt.poke_flag(0, 8)  # one ahead is legal: a peer may already have signalled the next barrier
+    rt.wait_only(1, 7, 50, stream)
+    torch.cuda.synchronize()
+    assert rt.read_status()[0] == 0
+    rt.destroy_arena()
+
+
+def test_checked_build_reports_out_of_range_stores():
+    """The library variant compiled with the per-store range check (JD_B200_BOUNDS=1) runs a correct plan
+    cleanly and turns a descriptor that claims too small a destination into a BOUNDS status, skipping
+    the stores instead of performing them."""
+    import os
+    import subprocess
+    import sys
+
+    code = r"""
+import torch, jaxdecomp_b200 as jd
+from jaxdecomp_b200 import native
+from jaxdecomp_b200.ops import passes, plan
+nat = native.require()
+assert nat.BOUNDS_CHECK_BUILD
+dev = torch.device('cuda', 0)
+x = torch.randn(32, 64, 128, device=dev, dtype=torch.complex64)
+k = jd.pfft3d(x, backend='b200')
+ref = torch.fft.fftn(x).permute(1, 2, 0)
+assert ((k - ref).abs().max() / ref.abs().max()).item() < 3e-6
+from jaxdecomp_b200.ops import b200_backend
+b200_backend.check_status(jd.single_rank_mesh(), sync=True)
+steps = plan.fft_steps(jd.NO_DECOMP, False, True, native=True)
+specs, _ = passes.compile_passes(steps, x.shape, (1, 1), (0, 0))
+rt = nat.Runtime(1, 0)
+rt.create_arena(1 << 20)
+for sp in specs[:2]:
+    d = passes.fill_desc(nat, sp, 8, False, 1.0, 1, False, True)
+    out = torch.zeros(sp.out_shape, device=dev, dtype=torch.complex64)
+    d.in_ptr = x.data_ptr(); d.set_out(0, out.data_ptr())
+    d.out_limit = x.numel() // 2
+    nat.launch_pass_checked(d, torch.cuda.current_stream().cuda_stream, rt.status_device_ptr())
+    torch.cuda.synchronize()
+    st = rt.read_status()
+    assert nat.status_name(st[0]) == 'BOUNDS', st
+    flat = out.reshape(-1)
+    assert float(flat[: x.numel() // 2].abs().sum()) > 0 and float(flat[x.numel() // 2:].abs().sum()) == 0
+    rt.clear_status()
+print('checked build ok')
+"""
+    env = dict(os.environ, JD_B200_BOUNDS="1")
+    r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "checked build ok" in r.stdout, r.stdout + r.stderr
+
+
 def test_large_offsets_use_64bit_indexing():
     # 2048 x 1024 x 1024 complex64 = 16 GiB: element offsets exceed 2^31
     free, _ = torch.cuda.mem_get_info()
