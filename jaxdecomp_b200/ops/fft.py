@@ -64,14 +64,32 @@ def _run(x: torch.Tensor, mesh, steps, inverse: bool, scale: float, backend: str
     return y
 
 
+def _vmap_leading(fn_apply, in_dims, x, args):
+    """Batching rule shared by the ops of this package: move the mapped dimension to the front, fold
+    all leading dimensions into the one batch dimension the kernels take, run the op once and unfold
+    (the reference's rule moves the batch axis to 0 and recurses, ``_src/jax/fft.py:549-573``)."""
+    bd = in_dims[0]
+    if bd is None:
+        return fn_apply(x, *args), None
+    x = x.movedim(bd, 0)
+    lead = tuple(x.shape[:-3])
+    y = fn_apply(x.reshape((-1,) + tuple(x.shape[-3:])).contiguous(), *args)
+    return y.reshape(lead + tuple(y.shape[-3:])), 0
+
+
 class _DistFFT(torch.autograd.Function):
-    """y = scale * (un-normalised forward or inverse pipeline)(x)."""
+    """y = scale * (un-normalised forward or inverse pipeline)(x).  Written in the form that
+    ``torch.func`` transforms need (``setup_context`` apart from ``forward``, a ``vmap`` rule), so that
+    ``vmap``, ``jacfwd`` and ``jacrev`` work through it like ``grad`` does."""
 
     @staticmethod
-    def forward(ctx, x, mesh, inverse, contiguous, scale, backend, pencil_type):
-        ctx.args = (mesh, inverse, contiguous, scale, backend, pencil_type)
+    def forward(x, mesh, inverse, contiguous, scale, backend, pencil_type):
         steps = _plan.fft_steps(pencil_type, inverse, contiguous, native=(backend == "b200"))
         return _run(x, mesh, steps, inverse, scale, backend, contiguous)
+
+    @staticmethod
+    def setup_context(ctx, inputs, output):
+        ctx.args = tuple(inputs[1:])
 
     @staticmethod
     def backward(ctx, g):
@@ -84,7 +102,11 @@ class _DistFFT(torch.autograd.Function):
     @staticmethod
     def jvp(ctx, t, *_):
         mesh, inverse, contiguous, scale, backend, pencil_type = ctx.args
-        return _DistFFT.apply(t, mesh, inverse, contiguous, scale, backend, pencil_type)
+        return _DistFFT.apply(t.contiguous(), mesh, inverse, contiguous, scale, backend, pencil_type)
+
+    @staticmethod
+    def vmap(info, in_dims, x, *args):
+        return _vmap_leading(_DistFFT.apply, in_dims, x, args)
 
 
 def _do_pfft(x, inverse: bool, norm, backend: str):
@@ -99,7 +121,15 @@ def _do_pfft(x, inverse: bool, norm, backend: str):
     names = mesh.decomp_axis_names
     spec = st.spatial_spec
     steps = _plan.fft_steps(pt, inverse, contiguous)
-    if not inverse:
+    if plain:
+        # a plain local block is taken to be in the layout the op expects: an X-pencil for the forward
+        # transform, the forward transform's output layout for the inverse
+        a0, a1 = names
+        spec = (a0 if mesh.pdims[0] > 1 else None, a1 if mesh.pdims[1] > 1 else None, None)
+        if inverse:
+            fwd = _plan.fft_steps(pt, False, contiguous)
+            _, spec = _plan.propagate(fwd, (mesh.pdims[0] * mesh.pdims[1],) * 3, spec, mesh.pdims, names)
+    elif not inverse:
         validate_spec_matches_mesh(spec, mesh)
     else:
         _plan.check_input_spec(steps, spec, mesh.pdims, names)

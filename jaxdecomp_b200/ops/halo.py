@@ -48,9 +48,12 @@ def _accumulate(g, mesh, extents, periods, backend):
 
 class _HaloExchange(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, mesh, extents, periods, backend, compat):
-        ctx.args = (mesh, extents, periods, backend, compat)
+    def forward(x, mesh, extents, periods, backend, compat):
         return _exchange(x, mesh, extents, periods, backend)
+
+    @staticmethod
+    def setup_context(ctx, inputs, output):
+        ctx.args = tuple(inputs[1:])
 
     @staticmethod
     def backward(ctx, g):
@@ -64,14 +67,23 @@ class _HaloExchange(torch.autograd.Function):
     @staticmethod
     def jvp(ctx, t, *_):
         mesh, extents, periods, backend, compat = ctx.args
-        return _HaloExchange.apply(t, mesh, extents, periods, backend, compat)
+        return _HaloExchange.apply(t.contiguous(), mesh, extents, periods, backend, compat)
+
+    @staticmethod
+    def vmap(info, in_dims, x, *args):
+        from .fft import _vmap_leading
+
+        return _vmap_leading(_HaloExchange.apply, in_dims, x, args)
 
 
 class _HaloAccumulate(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, g, mesh, extents, periods, backend):
-        ctx.args = (mesh, extents, periods, backend)
+    def forward(g, mesh, extents, periods, backend):
         return _accumulate(g, mesh, extents, periods, backend)
+
+    @staticmethod
+    def setup_context(ctx, inputs, output):
+        ctx.args = tuple(inputs[1:])
 
     @staticmethod
     def backward(ctx, gg):
@@ -79,6 +91,17 @@ class _HaloAccumulate(torch.autograd.Function):
         # the adjoint of the adjoint is the exchange itself
         y = _HaloExchange.apply(gg.contiguous(), mesh, extents, periods, backend, False)
         return y, None, None, None, None
+
+    @staticmethod
+    def jvp(ctx, t, *_):
+        mesh, extents, periods, backend = ctx.args
+        return _HaloAccumulate.apply(t.contiguous(), mesh, extents, periods, backend)
+
+    @staticmethod
+    def vmap(info, in_dims, x, *args):
+        from .fft import _vmap_leading
+
+        return _vmap_leading(_HaloAccumulate.apply, in_dims, x, args)
 
 
 def _effective_extents(mesh, extents):

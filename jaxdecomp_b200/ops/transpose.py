@@ -30,9 +30,12 @@ def _run(x, mesh, kind, contiguous, backend):
 
 class _Transpose(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, mesh, kind, contiguous, backend):
-        ctx.args = (mesh, kind, contiguous, backend)
+    def forward(x, mesh, kind, contiguous, backend):
         return _run(x, mesh, kind, contiguous, backend)
+
+    @staticmethod
+    def setup_context(ctx, inputs, output):
+        ctx.args = tuple(inputs[1:])
 
     @staticmethod
     def backward(ctx, g):
@@ -42,7 +45,13 @@ class _Transpose(torch.autograd.Function):
     @staticmethod
     def jvp(ctx, t, *_):
         mesh, kind, contiguous, backend = ctx.args
-        return _Transpose.apply(t, mesh, kind, contiguous, backend)
+        return _Transpose.apply(t.contiguous(), mesh, kind, contiguous, backend)
+
+    @staticmethod
+    def vmap(info, in_dims, x, *args):
+        from .fft import _vmap_leading
+
+        return _vmap_leading(_Transpose.apply, in_dims, x, args)
 
 
 def transpose(x, kind: str, backend: str = "auto"):

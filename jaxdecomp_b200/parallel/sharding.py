@@ -389,7 +389,13 @@ def shard(global_array: torch.Tensor, mesh: Mesh, spec=None) -> ShardedTensor:
 def as_sharded(x, mesh: Optional[Mesh] = None, spec=None) -> Tuple[ShardedTensor, bool]:
     """Normalise an op input.  Returns ``(sharded, was_plain)``: plain tensors
     are interpreted as the local block under the active mesh (``with mesh:`` or
-    :func:`set_mesh`), or as a complete array when there is no mesh."""
+    :func:`set_mesh`), in the layout the op expects.  Without an active mesh a
+    plain tensor is a complete array on a mesh of one rank -- unless the process
+    belongs to a job of several ranks: a tensor without sharding information
+    would then be transformed by every rank on its own, which is never what a
+    distributed op is called for, so this raises (the analogue of the reference's
+    diagnostics for unsharded operands, ``src/jaxdecomp/_src/error.py:1-18``).
+    Use ``with jd.single_rank_mesh():`` to transform a replicated array on purpose."""
     if isinstance(x, ShardedTensor):
         return x, False
     if not isinstance(x, torch.Tensor):
@@ -397,6 +403,12 @@ def as_sharded(x, mesh: Optional[Mesh] = None, spec=None) -> Tuple[ShardedTensor
     if mesh is None:
         mesh = current_mesh()
     if mesh is None:
+        import torch.distributed as dist
+
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+            from ..utils.errors import error_unsharded_operand
+
+            raise error_unsharded_operand("distributed op")
         from .mesh import single_rank_mesh
 
         mesh = single_rank_mesh()

@@ -60,7 +60,8 @@ def error_unsharded_operand(op: str) -> ShardingError:
     fully replicated tensor while a multi-rank mesh is active (the analogue of
     the reference's jacfwd/jacrev diagnostics)."""
     return ShardingError(
-        f"{op}: the operand carries no sharding information but the active mesh spans more than "
-        "one rank. Wrap the local block in a ShardedTensor (or call the op under `with mesh:` with "
-        "the local block of an X-pencil) so that the global shape and spec are known."
+        f"{op}: the operand is a plain tensor without sharding information, no mesh is active, and this "
+        "process is one of several ranks. Wrap the local block in a ShardedTensor, or call the op under "
+        "`with mesh:` with the local block in the layout the op expects; use `with jd.single_rank_mesh():` "
+        "to transform a replicated array on every rank on purpose."
     )

@@ -68,7 +68,18 @@ def _worker(rank: int, world: int, port: int, backend: str, fn: Callable, args: 
 
 
 def run_ranks(fn: Callable, world: int, *args, backend: str = "gloo", env: dict = None, timeout: float = 600.0) -> None:
-    """Run ``fn(rank, world, *args)`` on ``world`` processes; raise if any fails."""
+    """Run ``fn(rank, world, *args)`` on ``world`` processes; raise if any fails.  The rendezvous port
+    is picked by binding to port 0 and releasing it, so another process can take it in between: a run
+    that fails because the address is in use is repeated once on a fresh port."""
+    try:
+        _run_ranks_once(fn, world, args, backend, env, timeout)
+    except Exception as e:  # noqa: BLE001
+        if "EADDRINUSE" not in str(e) and "address already in use" not in str(e).lower():
+            raise
+        _run_ranks_once(fn, world, args, backend, env, timeout)
+
+
+def _run_ranks_once(fn: Callable, world: int, args: tuple, backend: str, env: dict, timeout: float) -> None:
     port = free_port()
     ctx = mp.start_processes(_worker, args=(world, port, backend, fn, args, env or {}), nprocs=world, join=False,
                              start_method="spawn")

@@ -218,3 +218,51 @@ def _barrier_worker(rank, world):
 @pytest.mark.skipif(_ngpu() < 2, reason="needs at least two GPUs")
 def test_signal_barrier_many_rounds():
     run_ranks(_barrier_worker, 2, backend="nccl", env={"NCCL_NVLS_ENABLE": "0"}, timeout=300)
+
+
+def _abort_worker(rank, world):
+    """A barrier that one rank joins late (host-side delay, 100 ms budget): the waiting rank records a
+    time-out and marks the whole group as aborted, the late rank learns of it in its own barrier, later
+    passes return at entry instead of computing on incomplete data, and finalize() + a fresh arena
+    bring the mesh back."""
+    import time
+
+    from jaxdecomp_b200.ops import b200_backend
+    from jaxdecomp_b200.utils.errors import PeerAbortedError, PeerTimeoutError
+
+    dev = torch.device("cuda", rank)
+    mesh = jd.make_mesh((1, world), ("z", "y"))
+    rt = b200_backend.get_runtime(mesh)
+    rt.ensure_arena(1 << 22)
+    x = jd.ShardedTensor(torch.randn((32, 64 // world, 128), device=dev, dtype=torch.complex64), mesh)
+    good = jd.pfft3d(x, backend="b200").local.clone()
+    torch.cuda.synchronize()
+    rt.rt.set_timeout_ms(100)
+    stream = torch.cuda.current_stream().cuda_stream
+    torch.distributed.barrier()
+    if rank == 1:
+        time.sleep(1.0)  # joins the barrier long after the other rank's budget has run out
+    rt.rt.barrier(stream)
+    torch.cuda.synchronize()
+    torch.distributed.barrier()
+    assert rt.rt.peek_flag(rt.nat.FLAG_ABORT_WORD) == 1  # set by rank 0 on every rank
+    with pytest.raises(PeerTimeoutError if rank == 0 else PeerAbortedError):
+        rt.check_status()
+    # kernels launched now return at entry; nothing waits, nothing faults, the context stays usable
+    before = rt.rt.launches()
+    jd.pfft3d(x, backend="b200")
+    torch.cuda.synchronize()
+    assert rt.rt.launches() > before
+    try:
+        rt.check_status()
+    except (PeerTimeoutError, PeerAbortedError):
+        pass
+    jd.finalize()  # collective: frees the aborted arena
+    again = jd.pfft3d(x, backend="b200").local
+    assert torch.equal(again, good)
+    b200_backend.check_status(mesh, sync=True)
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs at least two GPUs")
+def test_late_rank_aborts_the_group_and_finalize_recovers():
+    run_ranks(_abort_worker, 2, backend="nccl", env={"NCCL_NVLS_ENABLE": "0"}, timeout=300)
