@@ -266,3 +266,41 @@ def _abort_worker(rank, world):
 @pytest.mark.skipif(_ngpu() < 2, reason="needs at least two GPUs")
 def test_late_rank_aborts_the_group_and_finalize_recovers():
     run_ranks(_abort_worker, 2, backend="nccl", env={"NCCL_NVLS_ENABLE": "0"}, timeout=300)
+
+
+def _nested_worker(rank, world):
+    """Native backend on a 3-D mesh: the leading mesh axis splits a batch into independent groups of
+    2x2 GPUs, each op also carries a local batch dimension; everything against the baseline backend."""
+    from jaxdecomp_b200.ops import b200_backend
+
+    dev = torch.device("cuda", rank)
+    mesh = jd.Mesh((world // 4, 2, 2), ("c", "z", "y"))
+    grp = mesh.coords[0]
+    g = torch.Generator(device=dev).manual_seed(100 + grp)
+    xg = torch.complex(torch.randn((3, 64, 128, 256), generator=g, device=dev),
+                       torch.randn((3, 64, 128, 256), generator=g, device=dev))
+    x = jd.shard(xg, mesh, (None, "z", "y", None))
+    k = jd.pfft3d(x, backend="b200")
+    kr = jd.pfft3d(x, backend="torch")
+    assert tuple(k.spec) == tuple(kr.spec) and _rel(k.local, kr.local) < 3e-6
+    assert _rel(jd.pifft3d(k, backend="b200").local, x.local) < 3e-5
+    y = jd.transposeXtoY(x, backend="b200")
+    assert torch.equal(y.local, jd.transposeXtoY(x, backend="torch").local)
+    z = jd.transposeYtoZ(y, backend="b200")
+    assert torch.equal(z.local, jd.transposeYtoZ(y, backend="torch").local)
+    assert torch.equal(jd.transposeYtoX(jd.transposeZtoY(z, backend="b200"), backend="b200").local, x.local)
+    blk = jd.ShardedTensor(x.local.real.contiguous(), mesh, x.spec)
+    assert torch.equal(jd.halo_exchange(blk, (2, 2), (True, False), backend="b200").local,
+                       jd.halo_exchange(blk, (2, 2), (True, False), backend="torch").local)
+    torch.testing.assert_close(jd.halo_accumulate(blk, (2, 2), (True, True), backend="b200").local,
+                               jd.halo_accumulate(blk, (2, 2), (True, True), backend="torch").local)
+    with mesh:
+        kv = torch.func.vmap(lambda v: jd.pfft3d(v, backend="b200"))(x.local)
+    assert torch.equal(kv, k.local)
+    b200_backend.check_status(mesh, sync=True)
+
+
+@pytest.mark.skipif(_ngpu() < 4, reason="needs at least four GPUs")
+def test_native_backend_on_nested_mesh():
+    world = 8 if _ngpu() >= 8 else 4
+    run_ranks(_nested_worker, world, backend="nccl", env=_ENV, timeout=600)
