@@ -105,6 +105,19 @@ PYBIND11_MODULE(_jdb200, m) {
         d.out[p] = P(v);
       })
       .def("get_out", [](const PassDesc& d, int p) { return (uintptr_t)d.out[p]; })
+      // fused input multiplier: n = global extents of the original axes, off / axis = global offset and original
+      // axis of the role axes (c, t, o), kfac = 2*pi / box length per original axis
+      .def("set_mul", [](PassDesc& d, int mode, const std::vector<int>& n, const std::vector<int>& off,
+                         const std::vector<int>& axis, const std::vector<double>& kfac) {
+        if (n.size() != 3 || off.size() != 3 || axis.size() != 3 || kfac.size() != 3) throw py::value_error("set_mul: 3-vectors");
+        d.mul_mode = mode;
+        for (int i = 0; i < 3; ++i) {
+          d.mul.n[i] = n[i];
+          d.mul.off[i] = off[i];
+          d.mul.axis[i] = axis[i];
+          d.mul.kfac[i] = kfac[i];
+        }
+      })
       .def("copy", [](const PassDesc& d) { return d; })
       // the pass restricted to [lo, lo + len) of its t (role 2) or o (role 3) axis; in_ptr must be set
       .def("restricted", [](const PassDesc& d, int role, int lo, int len) {
@@ -124,6 +137,7 @@ PYBIND11_MODULE(_jdb200, m) {
     d.status = P(status);
     raise_on(launch_pass(d, P(stream), (StatusBlock*)P(status)), "launch_pass");
   });
+  m.def("fast_pass_eligible", [](const PassDesc& d) { return fast_pass_eligible(d); });
   m.def("pass_threads", &pass_threads);
   m.def("pass_smem_bytes", &pass_smem_bytes);
   m.def("get_fft_tables", [](int C, int M, int elem_bytes, bool device) {
@@ -242,7 +256,7 @@ PYBIND11_MODULE(_jdb200, m) {
   // ---- particle-mesh and k-space kernels -------------------------------------------------------------------
   m.def("cic", [](int op, long long n, std::vector<int> S, std::vector<int> wrap, std::vector<int> grid,
                   std::vector<float> origin, float wscalar, uintptr_t pos, uintptr_t weight, uintptr_t mesh, uintptr_t out,
-                  uintptr_t stream) {
+                  uintptr_t stream, bool planar) {
     if (S.size() != 3 || wrap.size() != 3 || grid.size() != 3 || origin.size() != 3) throw py::value_error("cic: 3-vectors expected");
     CicArgs a;
     a.n = n;
@@ -251,12 +265,14 @@ PYBIND11_MODULE(_jdb200, m) {
     a.g0 = grid[0]; a.g1 = grid[1]; a.g2 = grid[2];
     a.o0 = origin[0]; a.o1 = origin[1]; a.o2 = origin[2];
     a.wscalar = wscalar;
+    a.planar = planar ? 1 : 0;
     int rc;
     if (op == 0) rc = launch_cic_paint(a, (const float*)P(pos), (const float*)P(weight), (float*)P(mesh), P(stream));
     else if (op == 1) rc = launch_cic_readout(a, (const float*)P(pos), (const float*)P(mesh), (float*)P(out), P(stream));
     else rc = launch_cic_paint_grad_pos(a, (const float*)P(pos), (const float*)P(weight), (const float*)P(mesh), (float*)P(out), P(stream));
     raise_on(rc, "cic");
-  });
+  }, py::arg("op"), py::arg("n"), py::arg("S"), py::arg("wrap"), py::arg("grid"), py::arg("origin"), py::arg("wscalar"),
+     py::arg("pos"), py::arg("weight"), py::arg("mesh"), py::arg("out"), py::arg("stream"), py::arg("planar") = false);
   m.def("kspace", [](int mode, std::vector<int> L, std::vector<int> off, std::vector<int> N, std::vector<float> box,
                      std::vector<float> prm, int ntable, uintptr_t table, uintptr_t in, uintptr_t out0, uintptr_t out1,
                      uintptr_t out2, uintptr_t stream) {

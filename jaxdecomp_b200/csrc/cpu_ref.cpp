@@ -170,7 +170,19 @@ int validate_pass(const PassDesc& d) {
     return JD_ERR_INVALID_ARG;
   }
   if (d.elem_bytes != 4 && d.elem_bytes != 8 && d.elem_bytes != 16) return JD_ERR_INVALID_ARG;
-  if (d.mul_mode != 0 || d.mul != nullptr) return JD_ERR_INVALID_ARG;  // reserved fields
+  if (d.mul_mode != JD_MUL_NONE) {
+    // fused input multiplier: complex data, three batch entries (one per displacement component), rows read
+    // element by element (no bulk fetch, no direct-from-global first stage of the mixed-radix kernels)
+    if (d.mul_mode != JD_MUL_DISPLACEMENT || d.elem_bytes == 4 || d.B != 3 || d.use_bulk || d.fft_mode == JD_COPY ||
+        d.fft_mode == JD_FFT_MIXED)
+      return JD_ERR_INVALID_ARG;
+    int seen = 0;
+    for (int r = 0; r < 3; ++r) {
+      if (d.mul.axis[r] < 0 || d.mul.axis[r] > 2 || d.mul.n[r] < 1 || d.mul.off[r] < 0) return JD_ERR_INVALID_ARG;
+      seen |= 1 << d.mul.axis[r];
+    }
+    if (seen != 7) return JD_ERR_INVALID_ARG;
+  }
   if (d.load_t_contig ? d.is_t != 1 : d.is_c != 1) return JD_ERR_INVALID_ARG;
   if (d.store_t_contig ? d.os_t != 1 : d.os_c != 1) return JD_ERR_INVALID_ARG;
   if (d.fft_mode == JD_COPY) {

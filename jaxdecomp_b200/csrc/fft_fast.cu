@@ -262,6 +262,10 @@ __device__ __forceinline__ void fast_tile(const PassDesc& d, cx<R>* sm, int tile
 #pragma unroll
     for (int k = 0; k < 16; ++k) a[k] = src[k * UPR];
   }
+  if (d.mul_mode != JD_MUL_NONE) {
+#pragma unroll
+    for (int k = 0; k < 16; ++k) a[k] = apply_mul(d, a[k], j + k * UPR, t0 + row, o, b);
+  }
   if (inv) {
 #pragma unroll
     for (int k = 0; k < 16; ++k) a[k] = cswap(a[k]);

@@ -76,8 +76,9 @@ struct CicArgs {
   int32_t g0, g1, g2;        // lattice of initial positions (grid mode: pos holds displacements), or 0
   float o0, o1, o2;          // offset of the lattice inside the block
   float wscalar;             // weight of every particle when no per-particle weights are given
+  int32_t planar;            // 0: pos is [n, 3]; 1: pos is three planes [3, n] (gradients use the same layout)
 };
-// pos: [n,3] float32 positions (or displacements in grid mode) in cell units
+// pos: [n,3] (or, planar, [3,n]) float32 positions (or displacements in grid mode) in cell units
 int launch_cic_paint(const CicArgs& a, const float* pos, const float* weight, float* mesh, void* stream);
 int launch_cic_readout(const CicArgs& a, const float* pos, const float* mesh, float* out, void* stream);
 int launch_cic_paint_grad_pos(const CicArgs& a, const float* pos, const float* weight, const float* gmesh, float* gpos,

@@ -40,6 +40,22 @@ namespace jdb {
 // then the log2 of the next power of two >= M (only used to split loop counters into row and column).
 enum FftMode : int32_t { JD_COPY = 0, JD_FFT_POW2 = 1, JD_FFT_BLUESTEIN = 2, JD_FFT_MIXED = 3 };
 
+// Pointwise Fourier-space multiplier applied to the input of a pass, so that an operator such as
+// "i k_d / k^2" costs no pass over memory of its own (the reference gets the same effect from XLA
+// fusing the element-wise expression of examples/lpt_nbody_demo.py:120-133 into its neighbours).
+// The wave number along original axis a at global index g is kfac[a] * (g < (n[a]+1)/2 ? g : g - n[a]).
+struct MulDesc {
+  int32_t n[3];     // global extents of the original axes 0, 1, 2
+  int32_t off[3];   // global index of local index 0 along the role axes c, t, o
+  int32_t axis[3];  // original axis that the role axes c, t, o run along
+  double kfac[3];   // 2*pi / box length of the original axes
+};
+
+enum MulMode : int32_t {
+  JD_MUL_NONE = 0,
+  JD_MUL_DISPLACEMENT = 1,  // batch entry b (0..2) of the pass reads in * i * k_b / |k|^2 (0 at k = 0)
+};
+
 struct PassDesc {
   // strides in elements
   long long is_c, is_t, is_o, is_b;
@@ -57,8 +73,7 @@ struct PassDesc {
   int32_t load_t_contig;  // 1: input is contiguous along t (is_t == 1), else along c
   int32_t store_t_contig; // 1: output is contiguous along t (os_t == 1), else along c
   int32_t use_bulk;       // 1: fetch rows with bulk async copies (needs 16-byte aligned rows)
-  int32_t mul_mode;       // reserved for a fused pointwise multiplier in the store; must be 0 (descriptors with
-                          // another value are rejected by validate_pass)
+  int32_t mul_mode;       // MulMode: pointwise multiplier applied to every element as it is read
   int32_t vec_in;         // 1: 8-byte elements may be loaded two at a time (16-byte accesses)
   int32_t vec_out;        // 1: 8-byte elements may be stored two at a time
   int32_t intra_pad;      // 1: rows carry two unused slots after every 16 columns (bank-conflict-free FFT exchanges)
@@ -74,7 +89,7 @@ struct PassDesc {
   const void* tw_stage;   // per-stage twiddle records of the specialised power-of-two kernel (fft_fast_plan.h), or null
   const void* chirp;      // Bluestein: C entries exp(-i*pi*n^2/C)
   const void* bhat;       // Bluestein: M entries FFT_M(conj chirp, wrapped) / M
-  const void* mul;        // reserved (see mul_mode); must be null
+  MulDesc mul;            // geometry for mul_mode != JD_MUL_NONE
   const uint32_t* abort_word;  // device word of this rank that a failed cross-rank wait sets (signal.cu); blocks
                                // return at entry when it is non-zero; null: not checked
   long long out_limit;    // elements each destination buffer holds; checked per store by the CPU emulation and by

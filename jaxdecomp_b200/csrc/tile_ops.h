@@ -111,8 +111,40 @@ JD_HD int tile_cols(const PassDesc& d, int c0) {
   return (d.C - c0) < d.Cc ? (d.C - c0) : d.Cc;
 }
 
+// Fused input multiplier (PassDesc::mul_mode) for the element at local indices (c, t, o) of batch b.
 template <typename E>
-JD_HD E prepare_value(const PassDesc& d, E v, int c) {
+JD_HD E apply_mul(const PassDesc& d, E v, int c, int t, int o, int b) {
+  if constexpr (elem_traits<E>::is_complex) {
+    using R = typename elem_traits<E>::real;
+    if (d.mul_mode == JD_MUL_DISPLACEMENT) {
+      const MulDesc& m = d.mul;
+      const int idx[3] = {c, t, o};
+      R kv[3] = {0, 0, 0};
+      R kk = 0;
+#if defined(__CUDA_ARCH__)
+#pragma unroll
+#endif
+      for (int r = 0; r < 3; ++r) {
+        const int a = m.axis[r];
+        const int g = m.off[r] + idx[r];
+        const int f = g < (m.n[a] + 1) / 2 ? g : g - m.n[a];
+        const R k = (R)m.kfac[a] * (R)f;
+        kv[a] = k;
+        kk += k * k;
+      }
+      const R s = kk > (R)0 ? kv[b] / kk : (R)0;
+      // i * s * (x + i y) = s * (-y + i x)
+      v = E{-v.y * s, v.x * s};
+    }
+  }
+  return v;
+}
+
+// What a freshly loaded element goes through before it enters the tile: the fused multiplier (on the true
+// value), the conjugation trick of inverse transforms, the chirp of Bluestein's algorithm.
+template <typename E>
+JD_HD E prepare_value(const PassDesc& d, E v, int c, int t, int o, int b) {
+  if (d.mul_mode != JD_MUL_NONE) v = apply_mul(d, v, c, t, o, b);
   if constexpr (elem_traits<E>::is_complex) {
     if (d.inverse) v = cswap(v);
     if (d.fft_mode == JD_FFT_BLUESTEIN) v = cmul(v, ((const E*)d.chirp)[c]);
@@ -141,8 +173,8 @@ JD_HD void tile_load(const PassDesc& d, E* tile, int o, int t0, int c0, int b, i
         E v0 = zero, v1 = zero;
         if (c < cols && t0 + t < d.Tn) {
           const pair_of<E> p = *(const pair_of<E>*)(in + (long long)(c0 + c) * d.is_c + (t0 + t));
-          v0 = prepare_value(d, p.a, c);
-          v1 = prepare_value(d, p.b, c);
+          v0 = prepare_value(d, p.a, c0 + c, t0 + t, o, b);
+          v1 = prepare_value(d, p.b, c0 + c, t0 + t + 1, o, b);
         }
         const int col = padidx(c, pad);
         tile[t * d.pitch + col] = v0;
@@ -154,7 +186,7 @@ JD_HD void tile_load(const PassDesc& d, E* tile, int o, int t0, int c0, int b, i
         if (c >= wlim) continue;
         E v = zero;
         if (c < cols && t0 + t < d.Tn)
-          v = prepare_value(d, in[(long long)(c0 + c) * d.is_c + (long long)(t0 + t) * d.is_t], c);
+          v = prepare_value(d, in[(long long)(c0 + c) * d.is_c + (long long)(t0 + t) * d.is_t], c0 + c, t0 + t, o, b);
         tile[t * d.pitch + padidx(c, pad)] = v;
       }
     }
@@ -170,8 +202,8 @@ JD_HD void tile_load(const PassDesc& d, E* tile, int o, int t0, int c0, int b, i
         p.b = zero;
         if (c < cols && t0 + t < d.Tn) {
           p = *(const pair_of<E>*)(in + (long long)(t0 + t) * d.is_t + (c0 + c));
-          p.a = prepare_value(d, p.a, c);
-          p.b = prepare_value(d, p.b, c + 1);
+          p.a = prepare_value(d, p.a, c0 + c, t0 + t, o, b);
+          p.b = prepare_value(d, p.b, c0 + c + 1, t0 + t, o, b);
         }
         *(pair_of<E>*)(tile + t * d.pitch + padidx(c, pad)) = p;
       }
@@ -181,7 +213,7 @@ JD_HD void tile_load(const PassDesc& d, E* tile, int o, int t0, int c0, int b, i
         if (c >= wlim) continue;
         E v = zero;
         if (c < cols && t0 + t < d.Tn)
-          v = prepare_value(d, in[(long long)(t0 + t) * d.is_t + (long long)(c0 + c) * d.is_c], c);
+          v = prepare_value(d, in[(long long)(t0 + t) * d.is_t + (long long)(c0 + c) * d.is_c], c0 + c, t0 + t, o, b);
         tile[t * d.pitch + padidx(c, pad)] = v;
       }
     }

@@ -61,7 +61,8 @@ class LPTModel(torch.nn.Module):
         return (self.cfg.box_size,) * 3
 
     def displacement(self, noise: ShardedTensor):
-        """Return (delta_k, [psi_0, psi_1, psi_2]) with psi in cell units, real, X-pencil."""
+        """Return (delta_k, psi) with psi the three displacement fields in cell units, real, X-pencil,
+        stacked along a leading dimension."""
         cfg = self.cfg
         nc = cfg.nc
         delta_k = pfft3d(noise, backend=cfg.backend)
@@ -73,25 +74,25 @@ class LPTModel(torch.nn.Module):
         else:
             delta_k = kspace.apply_power_law(delta_k, self.box, cfg.amplitude, cfg.index,
                                              cfg.k_cut if cfg.k_cut is not None else k_nyq, norm)
-        pots = kspace.displacement_potentials(delta_k, self.box)
+        # one batched inverse transform for the three components (multiplier fused into its first pass on
+        # the native backend); the result stays planar, [3, l0, l1, l2], which is what the painter reads
         cells = nc / cfg.box_size * cfg.growth
-        psi = []
-        for p in pots:
-            real = pifft3d(p, backend=cfg.backend)
-            psi.append(real.local.real * cells)
+        psi = kspace.inverse_displacements(delta_k, self.box, backend=cfg.backend).local.real * cells
         return delta_k, psi
 
-    def paint(self, psi: Sequence[torch.Tensor]) -> ShardedTensor:
-        """Displace lattice particles by ``psi`` and paint them; returns the density (X-pencil)."""
+    def paint(self, psi) -> ShardedTensor:
+        """Displace lattice particles by ``psi`` (``[3, l0, l1, l2]`` or three blocks) and paint them;
+        returns the density (X-pencil)."""
         cfg = self.cfg
         hs = cfg.halo
         p0, p1 = self.mesh.pdims
         h0 = hs if p0 > 1 else 0
         h1 = hs if p1 > 1 else 0
-        l0, l1, l2 = psi[0].shape
-        disp = torch.stack(list(psi), dim=-1).contiguous()
-        padded = cic_paint(disp, (l0 + 2 * h0, l1 + 2 * h1, l2), wrap=(p0 == 1, p1 == 1, True), lattice=(l0, l1, l2),
-                           origin=(float(h0), float(h1), 0.0))
+        if not isinstance(psi, torch.Tensor):
+            psi = torch.stack(list(psi))
+        l0, l1, l2 = psi.shape[1:]
+        padded = cic_paint(psi.contiguous(), (l0 + 2 * h0, l1 + 2 * h1, l2), wrap=(p0 == 1, p1 == 1, True),
+                           lattice=(l0, l1, l2), origin=(float(h0), float(h1), 0.0), planar=True)
         st = ShardedTensor(padded, self.mesh)
         return halo_reduce(st, (h0, h1), (True, True), backend=cfg.backend)
 

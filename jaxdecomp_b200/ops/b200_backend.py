@@ -129,7 +129,8 @@ class MeshRuntime:
         coords[self.mesh.ndim - 2 + mesh_axis] = p
         return self.ranks.index(self.mesh.rank_of(coords))
 
-    def build_plan(self, key: str, steps: Sequence[Step], lshape, dtype, inverse: bool, scale: float, nbatch: int):
+    def build_plan(self, key: str, steps: Sequence[Step], lshape, dtype, inverse: bool, scale: float, nbatch: int,
+                   fused_mul=None):
         nat = self.nat
         eb = torch.empty((), dtype=dtype).element_size()
         coords = self.mesh.coords[-2:]
@@ -150,6 +151,15 @@ class MeshRuntime:
         for i, sp in enumerate(specs):
             remote = sp.npeers > 1
             d = _passes.fill_desc(nat, sp, eb, inverse, scale if i == last_fft else 1.0, nbatch, remote, True)
+            if fused_mul is not None and i == 0:
+                # the first pass reads one block for all three batch entries and multiplies entry b by
+                # i k_b / k^2 on the fly; dims of the rotated layout hold the original axes (1, 2, 0)
+                n_orig, offs, box = fused_mul
+                rot = (1, 2, 0)
+                d.set_mul(1, [int(v) for v in n_orig], [int(offs[a]) for a in sp.axes], [rot[a] for a in sp.axes],
+                          [2.0 * 3.141592653589793 / float(b) for b in box])
+                d.is_b = 0
+                d.use_bulk = 0
             st = nat.PlanStep()
             st.in_kind = cur_kind
             last = i == n - 1
@@ -186,15 +196,40 @@ class MeshRuntime:
         pid = self.rt.add_plan(key, plan_steps, slot_bytes)
         return pid, final_shape
 
-    def run_steps(self, x: torch.Tensor, steps: Sequence[Step], inverse: bool, scale: float) -> torch.Tensor:
+    def fused_mul_supported(self, steps: Sequence[Step], lshape, dtype) -> bool:
+        """True when the first pass of ``steps`` can carry the fused k-space multiplier: a power-of-two
+        transform of complex data (the kernels that read element by element)."""
+        eb = torch.empty((), dtype=dtype).element_size()
+        if eb not in (8, 16):
+            return False
+        specs, _ = _passes.compile_passes(steps, lshape, self.mesh.pdims, self.mesh.coords[-2:])
+        if not specs or not specs[0].fft:
+            return False
+        c = specs[0].ext[0]
+        return c >= 8 and (c & (c - 1)) == 0
+
+    def run_steps(self, x: torch.Tensor, steps: Sequence[Step], inverse: bool, scale: float,
+                  fused_mul=None) -> torch.Tensor:
+        """Execute a step list on a local block.  ``fused_mul = (n_orig, offsets, box)`` makes the result a
+        batch of three: entry b is the pipeline applied to ``x * i k_b / k^2`` (``x`` in the rotated layout of
+        ``pfft3d``, ``offsets`` the global indices of its first element), with the multiplier applied inside
+        the first pass instead of by a kernel of its own."""
         x = _aligned(x)
         nb = x.dim() - 3
         if nb not in (0, 1):
             raise ValueError("expected a 3-D block or a 4-D block with one leading batch dimension")
-        nbatch = x.shape[0] if nb else 1
-        lshape = tuple(x.shape[nb:])
+        if fused_mul is not None and nb:
+            raise ValueError("the fused multiplier takes a single 3-D block")
+        nbatch = x.shape[0] if nb else (3 if fused_mul is not None else 1)
+        if fused_mul is not None:
+            nb = 1
+            lshape = tuple(x.shape)
+        else:
+            lshape = tuple(x.shape[nb:])
         env = tuple(os.environ.get(k, "") for k in _TUNING_ENV)
-        pykey = (tuple(steps), lshape, x.dtype, bool(inverse), float(scale), nbatch, env, config.snapshot())
+        fkey = None if fused_mul is None else (tuple(fused_mul[0]), tuple(int(o) for o in fused_mul[1]),
+                                               tuple(float(b) for b in fused_mul[2]))
+        pykey = (tuple(steps), lshape, x.dtype, bool(inverse), float(scale), nbatch, env, config.snapshot(), fkey)
         hit = self._pycache.get(pykey)
         if hit is None:
             if not _passes._group_steps(steps, self.mesh.pdims):
@@ -202,7 +237,7 @@ class MeshRuntime:
             key = "|".join(map(str, pykey + (self.mesh.pdims, self.mesh.coords[-2:])))
             pid = self.rt.find_plan(key)
             if pid < 0:
-                pid, final_shape = self.build_plan(key, steps, lshape, x.dtype, inverse, scale, nbatch)
+                pid, final_shape = self.build_plan(key, steps, lshape, x.dtype, inverse, scale, nbatch, fused_mul)
                 self._shapes[pid] = final_shape
             hit = self._pycache[pykey] = (pid, self._shapes[pid], self.rt.plan_slot_bytes(pid))
         else:
@@ -305,8 +340,9 @@ def get_runtime(mesh: Mesh) -> MeshRuntime:
     return rt
 
 
-def run_steps(x: torch.Tensor, steps: Sequence[Step], mesh: Mesh, inverse: bool, scale: float) -> torch.Tensor:
-    return get_runtime(mesh).run_steps(x, steps, inverse, scale)
+def run_steps(x: torch.Tensor, steps: Sequence[Step], mesh: Mesh, inverse: bool, scale: float,
+              fused_mul=None) -> torch.Tensor:
+    return get_runtime(mesh).run_steps(x, steps, inverse, scale, fused_mul)
 
 
 def halo_exchange(x, extents, periods, mesh: Mesh, inplace: bool = False) -> torch.Tensor:

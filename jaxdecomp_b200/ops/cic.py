@@ -19,8 +19,8 @@ from typing import Optional, Sequence
 import torch
 
 
-def _positions(pos: torch.Tensor, lattice, origin) -> torch.Tensor:
-    p = pos.reshape(-1, 3)
+def _positions(pos: torch.Tensor, lattice, origin, planar: bool = False) -> torch.Tensor:
+    p = pos.reshape(3, -1).t() if planar else pos.reshape(-1, 3)
     if lattice is not None:
         g0, g1, g2 = lattice
         dev = p.device
@@ -83,7 +83,7 @@ def _grad_pos_torch(p, weight, gmesh, wrap):
     return g
 
 
-def _native_call(op, pos, weight, mesh_or_g, out, shape, wrap, lattice, origin, wscalar):
+def _native_call(op, pos, weight, mesh_or_g, out, shape, wrap, lattice, origin, wscalar, planar=False):
     from .. import native
 
     nat = native.require()
@@ -91,98 +91,104 @@ def _native_call(op, pos, weight, mesh_or_g, out, shape, wrap, lattice, origin, 
     nat.cic(op, n, [int(s) for s in shape], [int(bool(w)) for w in wrap],
             [int(g) for g in (lattice or (0, 0, 0))], [float(o) for o in origin], float(wscalar),
             pos.data_ptr(), 0 if weight is None else weight.data_ptr(), mesh_or_g.data_ptr(),
-            0 if out is None else out.data_ptr(), torch.cuda.current_stream().cuda_stream)
+            0 if out is None else out.data_ptr(), torch.cuda.current_stream().cuda_stream, bool(planar))
 
 
 def _use_native(t: torch.Tensor) -> bool:
     return t.is_cuda and t.dtype == torch.float32
 
 
-def _paint_impl(pos, weight, wscalar, shape, wrap, lattice, origin):
+def _paint_impl(pos, weight, wscalar, shape, wrap, lattice, origin, planar=False):
     if _use_native(pos):
         mesh = torch.zeros(shape, dtype=torch.float32, device=pos.device)
         _native_call(0, pos.contiguous(), None if weight is None else weight.contiguous(), mesh, None, shape, wrap,
-                     lattice, origin, wscalar)
+                     lattice, origin, wscalar, planar)
         return mesh
     w = weight.reshape(-1) if weight is not None else torch.as_tensor(wscalar, dtype=pos.dtype, device=pos.device)
-    return _paint_torch(_positions(pos, lattice, origin), w, tuple(shape), wrap)
+    return _paint_torch(_positions(pos, lattice, origin, planar), w, tuple(shape), wrap)
 
 
-def _readout_impl(pos, mesh, wrap, lattice, origin):
+def _readout_impl(pos, mesh, wrap, lattice, origin, planar=False):
     if _use_native(pos):
         out = torch.empty(pos.numel() // 3, dtype=torch.float32, device=pos.device)
-        _native_call(1, pos.contiguous(), None, mesh.contiguous(), out, mesh.shape, wrap, lattice, origin, 1.0)
+        _native_call(1, pos.contiguous(), None, mesh.contiguous(), out, mesh.shape, wrap, lattice, origin, 1.0, planar)
         return out
-    return _readout_torch(_positions(pos, lattice, origin), mesh, wrap)
+    return _readout_torch(_positions(pos, lattice, origin, planar), mesh, wrap)
 
 
-def _grad_pos_impl(pos, weight, wscalar, gmesh, wrap, lattice, origin):
+def _grad_pos_impl(pos, weight, wscalar, gmesh, wrap, lattice, origin, planar=False):
     if _use_native(pos):
         g = torch.empty_like(pos, memory_format=torch.contiguous_format)
         _native_call(2, pos.contiguous(), None if weight is None else weight.contiguous(), gmesh.contiguous(), g,
-                     gmesh.shape, wrap, lattice, origin, wscalar)
+                     gmesh.shape, wrap, lattice, origin, wscalar, planar)
         return g
     w = weight.reshape(-1) if weight is not None else torch.as_tensor(wscalar, dtype=pos.dtype, device=pos.device)
-    return _grad_pos_torch(_positions(pos, lattice, origin), w, gmesh, wrap).reshape(pos.shape)
+    g = _grad_pos_torch(_positions(pos, lattice, origin, planar), w, gmesh, wrap)
+    return (g.t() if planar else g).reshape(pos.shape)
 
 
 class _Paint(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, pos, weight, wscalar, shape, wrap, lattice, origin):
+    def forward(ctx, pos, weight, wscalar, shape, wrap, lattice, origin, planar=False):
         ctx.save_for_backward(pos, weight if weight is not None else pos.new_empty(0))
-        ctx.meta = (wscalar, tuple(shape), tuple(wrap), lattice, tuple(origin), weight is not None)
-        return _paint_impl(pos, weight, wscalar, shape, wrap, lattice, origin)
+        ctx.meta = (wscalar, tuple(shape), tuple(wrap), lattice, tuple(origin), weight is not None, planar)
+        return _paint_impl(pos, weight, wscalar, shape, wrap, lattice, origin, planar)
 
     @staticmethod
     def backward(ctx, g):
         pos, weight = ctx.saved_tensors
-        wscalar, shape, wrap, lattice, origin, has_w = ctx.meta
+        wscalar, shape, wrap, lattice, origin, has_w, planar = ctx.meta
         weight = weight if has_w else None
         g = g.contiguous()
         gpos = gw = None
         if ctx.needs_input_grad[0]:
-            gpos = _grad_pos_impl(pos, weight, wscalar, g, wrap, lattice, origin)
+            gpos = _grad_pos_impl(pos, weight, wscalar, g, wrap, lattice, origin, planar)
         if has_w and ctx.needs_input_grad[1]:
-            gw = _readout_impl(pos, g, wrap, lattice, origin).reshape(weight.shape)
-        return gpos, gw, None, None, None, None, None
+            gw = _readout_impl(pos, g, wrap, lattice, origin, planar).reshape(weight.shape)
+        return gpos, gw, None, None, None, None, None, None
 
 
 class _Readout(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, pos, mesh, wrap, lattice, origin):
+    def forward(ctx, pos, mesh, wrap, lattice, origin, planar=False):
         ctx.save_for_backward(pos, mesh)
-        ctx.meta = (tuple(wrap), lattice, tuple(origin))
-        return _readout_impl(pos, mesh, wrap, lattice, origin)
+        ctx.meta = (tuple(wrap), lattice, tuple(origin), planar)
+        return _readout_impl(pos, mesh, wrap, lattice, origin, planar)
 
     @staticmethod
     def backward(ctx, g):
         pos, mesh = ctx.saved_tensors
-        wrap, lattice, origin = ctx.meta
+        wrap, lattice, origin, planar = ctx.meta
         g = g.contiguous()
         gpos = gmesh = None
         if ctx.needs_input_grad[0]:
-            gpos = _grad_pos_impl(pos, g, 1.0, mesh, wrap, lattice, origin)
+            gpos = _grad_pos_impl(pos, g, 1.0, mesh, wrap, lattice, origin, planar)
         if ctx.needs_input_grad[1]:
-            gmesh = _paint_impl(pos, g, 1.0, mesh.shape, wrap, lattice, origin)
-        return gpos, gmesh, None, None, None
+            gmesh = _paint_impl(pos, g, 1.0, mesh.shape, wrap, lattice, origin, planar)
+        return gpos, gmesh, None, None, None, None
 
 
 def cic_paint(pos: torch.Tensor, mesh_shape: Sequence[int], weight: Optional[torch.Tensor] = None, value: float = 1.0,
               wrap: Sequence[bool] = (False, False, True), lattice: Optional[Sequence[int]] = None,
-              origin: Sequence[float] = (0.0, 0.0, 0.0)) -> torch.Tensor:
-    """Deposit particles onto a zero-initialised mesh of ``mesh_shape`` with trilinear weights."""
-    if pos.shape[-1] != 3:
-        raise ValueError("pos must have a trailing dimension of 3")
+              origin: Sequence[float] = (0.0, 0.0, 0.0), planar: bool = False) -> torch.Tensor:
+    """Deposit particles onto a zero-initialised mesh of ``mesh_shape`` with trilinear weights.
+
+    ``pos`` is ``[..., 3]``, or with ``planar=True`` three planes ``[3, ...]`` -- the layout in which a
+    batched inverse FFT returns the three displacement fields, so that they can be painted without
+    interleaving them first."""
+    if (pos.shape[0] if planar else pos.shape[-1]) != 3:
+        raise ValueError("pos must have a leading (planar) or trailing dimension of 3")
     lat = tuple(int(g) for g in lattice) if lattice is not None else None
     if lat is not None and lat[0] * lat[1] * lat[2] != pos.numel() // 3:
         raise ValueError("lattice does not match the number of particles")
     return _Paint.apply(pos, weight, float(value), tuple(int(s) for s in mesh_shape), tuple(bool(w) for w in wrap), lat,
-                        tuple(float(o) for o in origin))
+                        tuple(float(o) for o in origin), bool(planar))
 
 
 def cic_readout(pos: torch.Tensor, mesh: torch.Tensor, wrap: Sequence[bool] = (False, False, True),
-                lattice: Optional[Sequence[int]] = None, origin: Sequence[float] = (0.0, 0.0, 0.0)) -> torch.Tensor:
+                lattice: Optional[Sequence[int]] = None, origin: Sequence[float] = (0.0, 0.0, 0.0),
+                planar: bool = False) -> torch.Tensor:
     """Interpolate the mesh at the particle positions (adjoint of :func:`cic_paint`)."""
     lat = tuple(int(g) for g in lattice) if lattice is not None else None
-    out = _Readout.apply(pos, mesh, tuple(bool(w) for w in wrap), lat, tuple(float(o) for o in origin))
-    return out.reshape(pos.shape[:-1])
+    out = _Readout.apply(pos, mesh, tuple(bool(w) for w in wrap), lat, tuple(float(o) for o in origin), bool(planar))
+    return out.reshape(pos.shape[1:] if planar else pos.shape[:-1])

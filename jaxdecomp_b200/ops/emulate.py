@@ -41,7 +41,7 @@ def split_blocks(x: torch.Tensor, pdims: Sequence[int], spec_axes=(0, 1)) -> Lis
 
 
 def emulate_steps(blocks: List[torch.Tensor], steps: Sequence[Step], pdims: Sequence[int], inverse: bool = False,
-                  scale: float = 1.0, pipeline_chunks: int = 0) -> List[torch.Tensor]:
+                  scale: float = 1.0, pipeline_chunks: int = 0, fused_mul=None) -> List[torch.Tensor]:
     """Run a step list on the blocks of all ranks (row-major rank order) and
     return the per-rank results.
 
@@ -50,7 +50,10 @@ def emulate_steps(blocks: List[torch.Tensor], steps: Sequence[Step], pdims: Sequ
     is executed the way the pipelined executor does: chunk by chunk, the
     consumer's chunk k right after chunk k of all producers and *before* their
     chunk k+1 exists -- so a consumer chunk that read outside its producers'
-    chunk would see zeros and the result would differ."""
+    chunk would see zeros and the result would differ.
+
+    ``fused_mul = (n_orig, offsets_per_rank, box)`` runs the first pass with the fused k-space multiplier
+    (three batch entries read from the one input block, entry b multiplied by ``i k_b / k^2``)."""
     from .. import native as _native
 
     nat = _native.require()
@@ -62,6 +65,9 @@ def emulate_steps(blocks: List[torch.Tensor], steps: Sequence[Step], pdims: Sequ
     nbatch = 1
     if blocks[0].dim() == 4:
         nbatch = blocks[0].shape[0]
+    if fused_mul is not None:
+        assert blocks[0].dim() == 3
+        nbatch = 3
     compiled = []
     for r in range(world):
         coords = (r // p1, r % p1)
@@ -72,7 +78,7 @@ def emulate_steps(blocks: List[torch.Tensor], steps: Sequence[Step], pdims: Sequ
     cur = [b.contiguous() for b in blocks]
 
     def alloc(i):
-        full = ((nbatch,) if blocks[0].dim() == 4 else ()) + tuple(compiled[0][i].out_shape)
+        full = ((nbatch,) if (blocks[0].dim() == 4 or fused_mul is not None) else ()) + tuple(compiled[0][i].out_shape)
         return [torch.zeros(full, dtype=dtype) for _ in range(world)]
 
     def desc(i, r, src, dst_bufs):
@@ -81,6 +87,12 @@ def emulate_steps(blocks: List[torch.Tensor], steps: Sequence[Step], pdims: Sequ
         d = _passes.fill_desc(nat, sp, eb, inverse, scale if i == last_fft else 1.0, nbatch,
                               remote=sp.npeers > 1, device_tables=False)
         d.use_bulk = 0
+        if fused_mul is not None and i == 0:
+            n_orig, offs, box = fused_mul
+            rot = (1, 2, 0)
+            d.set_mul(1, [int(v) for v in n_orig], [int(offs[r][a]) for a in sp.axes], [rot[a] for a in sp.axes],
+                      [2.0 * 3.141592653589793 / float(b) for b in box])
+            d.is_b = 0
         d.in_ptr = src[r].data_ptr()
         for p in range(sp.npeers):
             if sp.mesh_axis is None:

@@ -188,3 +188,64 @@ def displacement_potentials(k: ShardedTensor, box: Sequence[float]):
     _check(k)
     ys = _Gradient.apply(k.local, _Geo(k), tuple(box))
     return tuple(ShardedTensor(y, k.mesh, k.spec, k.global_shape) for y in ys)
+
+
+class _InverseDisplacements(torch.autograd.Function):
+    """psi_b = scale * IFFT(i k_b / k^2 * delta_k), b = 0, 1, 2, as one batched inverse transform whose first
+    pass applies the multiplier while it reads ``delta_k`` (native backend), so the three potentials are
+    never written to memory."""
+
+    @staticmethod
+    def forward(x, kst, box, mesh, contiguous, scale, pencil_type):
+        from . import b200_backend
+        from . import plan as _plan
+
+        steps = _plan.fft_steps(pencil_type, True, contiguous, native=True)
+        (n0, n1, n2), offs, _ = _geometry(kst)
+        return b200_backend.run_steps(x, steps, mesh, True, scale, fused_mul=((n0, n1, n2), offs, box))
+
+    @staticmethod
+    def setup_context(ctx, inputs, output):
+        ctx.meta = tuple(inputs[1:])
+
+    @staticmethod
+    def backward(ctx, g):
+        from .fft import _DistFFT
+
+        kst, box, mesh, contiguous, scale, pencil_type = ctx.meta
+        # adjoint: the opposite pipeline on the three cotangents (one batched plan), then sum_b conj(i k_b / k^2)
+        gk = _DistFFT.apply(g.contiguous(), mesh, False, contiguous, scale, "b200", pencil_type)
+        return _GradientAdjoint.apply(gk[0], gk[1], gk[2], kst, box), None, None, None, None, None, None
+
+
+def inverse_displacements(k: ShardedTensor, box: Sequence[float], backend: str = "auto") -> ShardedTensor:
+    """The three displacement fields in real space, ``pifft3d(i k_d / k^2 * k)`` for the original axes
+    d = 0, 1, 2, stacked along a new leading dimension (complex; the imaginary parts vanish for the
+    transform of a real field).  Counterpart of the potentials-then-three-inverse-FFTs sequence of the
+    reference's example (``examples/lpt_nbody_demo.py:120-135``).  On the native backend this is one batched
+    plan with the multiplier fused into its first pass; elsewhere the potentials are formed first and
+    transformed as one batch."""
+    from ..utils.config import config
+    from .dispatch import resolve_backend
+    from .fft import _fft_norm, pifft3d
+
+    _check(k)
+    b = resolve_backend(backend, k.local)
+    mesh = k.mesh
+    gshape = k.global_shape[-3:]
+    if b == "b200" and k.local.dim() == 3 and bool(config.transpose_axis_contiguous):
+        from . import b200_backend
+        from . import plan as _plan
+
+        rt = b200_backend.get_runtime(mesh)
+        steps = _plan.fft_steps(mesh.pencil_type, True, True, native=True)
+        if rt.fused_mul_supported(steps, tuple(k.local.shape), k.local.dtype):
+            _plan.check_input_spec(steps, k.spatial_spec, mesh.pdims, mesh.decomp_axis_names)
+            _, out_spec = _plan.propagate(steps, tuple(k.local.shape), k.spatial_spec, mesh.pdims, mesh.decomp_axis_names)
+            scale = _fft_norm(gshape, True, "backward")
+            y = _InverseDisplacements.apply(k.local.contiguous(), _Geo(k), tuple(float(v) for v in box), mesh, True,
+                                            scale, mesh.pencil_type)
+            return ShardedTensor(y, mesh, (None,) + tuple(out_spec))
+    pots = displacement_potentials(k, box)
+    stacked = ShardedTensor(torch.stack([p.local for p in pots]), mesh, (None,) + tuple(k.spec))
+    return pifft3d(stacked, backend=backend)

@@ -45,6 +45,27 @@ def test_cic_kernels_match_cpu_reference():
     assert abs(float(a.sum()) - 10 * 12 * 16) < 1e-2
 
 
+def test_tiled_cic_paint_matches_the_plain_kernel_and_the_cpu(monkeypatch):
+    """Lattices that split into whole 8 x 8 x 32 bricks take the shared-memory kernel: small displacements
+    stay inside a brick's apron, large ones (up to 9 cells here) leave it and go to global memory directly,
+    and both wrap and drop at the block edge."""
+    g = torch.Generator().manual_seed(3)
+    lat = (16, 24, 64)
+    for scale, wrap, shape, origin in ((1.5, (False, False, True), (24, 32, 64), (4.0, 4.0, 0.0)),
+                                       (18.0, (True, True, True), (16, 24, 64), (0.0, 0.0, 0.0)),
+                                       (18.0, (False, False, True), (20, 28, 64), (2.0, 2.0, 0.0))):
+        disp = (torch.rand((*lat, 3), generator=g) - 0.5) * scale
+        w = torch.rand(lat, generator=g)
+        ref = cic_paint(disp.double(), shape, weight=w.double().reshape(-1), wrap=wrap, lattice=lat, origin=origin)
+        monkeypatch.setenv("JD_B200_CIC_TILED", "1")
+        tiled = cic_paint(disp.to(DEV), shape, weight=w.to(DEV).reshape(-1), wrap=wrap, lattice=lat, origin=origin)
+        monkeypatch.setenv("JD_B200_CIC_TILED", "0")
+        plain = cic_paint(disp.to(DEV), shape, weight=w.to(DEV).reshape(-1), wrap=wrap, lattice=lat, origin=origin)
+        monkeypatch.delenv("JD_B200_CIC_TILED")
+        torch.testing.assert_close(tiled.cpu().double(), ref, atol=5e-5, rtol=1e-4)
+        torch.testing.assert_close(tiled, plain, atol=5e-5, rtol=1e-4)
+
+
 def test_kspace_kernels_match_torch():
     mesh = jd.single_rank_mesh()
     x = torch.randn((16, 24, 32), generator=torch.Generator().manual_seed(1))
@@ -91,3 +112,28 @@ def test_lpt_step_and_gradient_on_gpu():
     assert err < 5e-3, float(err)
     dens = model(jd.ShardedTensor(noise_c.float().to(DEV), mesh))
     assert abs(float(dens.local.sum()) - 32 ** 3) < 1.0
+
+
+def test_fused_inverse_displacements_match_the_unfused_sequence():
+    """One batched inverse plan with the multiplier applied in its first pass against potentials formed by
+    the k-space kernel and transformed one by one; values and the gradient with respect to delta_k."""
+    from jaxdecomp_b200.ops import b200_backend
+
+    mesh = jd.single_rank_mesh()
+    box = (16.0, 12.0, 64.0)
+    x = torch.randn((32, 16, 128), device=DEV, generator=torch.Generator(device=DEV).manual_seed(4))
+    k = jd.pfft3d(jd.ShardedTensor(x, mesh), backend="b200")
+    kl = k.local.detach().clone().requires_grad_(True)
+    before = b200_backend.launches(mesh)
+    psi = kspace.inverse_displacements(jd.ShardedTensor(kl, mesh, k.spec), box, backend="b200")
+    assert b200_backend.launches(mesh) - before == 3          # three passes, no separate multiplier kernel
+    assert psi.local.shape == (3, 32, 16, 128)
+    kr = k.local.detach().clone().requires_grad_(True)
+    pots = kspace.displacement_potentials(jd.ShardedTensor(kr, mesh, k.spec), box)
+    ref = torch.stack([jd.pifft3d(p, backend="b200").local for p in pots])
+    torch.testing.assert_close(psi.local, ref, atol=2e-5, rtol=1e-4)
+    w = torch.randn(psi.local.shape, device=DEV, generator=torch.Generator(device=DEV).manual_seed(5))
+    (psi.local.real * w).sum().backward()
+    (ref.real * w).sum().backward()
+    torch.testing.assert_close(kl.grad, kr.grad, atol=2e-5, rtol=1e-4)
+    b200_backend.check_status(mesh, sync=True)

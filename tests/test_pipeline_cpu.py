@@ -155,3 +155,41 @@ def test_pipeline_protocol_withheld_chunk_signal_times_out_and_aborts_all():
     assert all(k <= 1 for (r, k, code) in log if code == OK)
     assert board.aborted == [1, 1, 1, 1]
     assert m.consumed_before_produced == 0
+
+
+@pytest.mark.parametrize("pdims", [(1, 1), (2, 2), (1, 4)])
+def test_fused_displacement_multiplier_in_the_first_inverse_pass(pdims):
+    """Entry b of the batched inverse plan reads delta_k * i k_b / k^2 (multiplier applied inside the first
+    pass): against the explicit potentials transformed with torch."""
+    import math
+
+    n = (16, 8, 32)
+    box = (10.0, 20.0, 30.0)
+    names = ("a0", "a1")
+    x = torch.randn(n, dtype=torch.complex128, generator=torch.Generator().manual_seed(9))
+    pt = pencil_type_from_pdims(pdims)
+    fwd = plan.fft_steps(pt, False, True, native=True)
+    kblocks = emulate.emulate_steps(emulate.split_blocks(x, pdims), fwd, pdims)
+    xspec = (names[0] if pdims[0] > 1 else None, names[1] if pdims[1] > 1 else None, None)
+    _, kspec = plan.propagate(fwd, kblocks[0].shape, xspec, pdims, names)
+    p0, p1 = pdims
+    offs = []
+    for r in range(p0 * p1):
+        c = (r // p1, r % p1)
+        offs.append([0 if s is None else c[names.index(s)] * kblocks[r].shape[ax] for ax, s in enumerate(kspec)])
+    inv = plan.fft_steps(pt, True, True, native=True)
+    outs = emulate.emulate_steps(kblocks, inv, pdims, True, 1.0 / x.numel(), fused_mul=(n, offs, box))
+    # oracle on the gathered spectrum
+    kf = [2 * math.pi / box[a] * torch.fft.fftfreq(n[a], d=1.0 / n[a], dtype=torch.float64) for a in range(3)]
+    k0, k1, k2 = kf[0].view(-1, 1, 1), kf[1].view(1, -1, 1), kf[2].view(1, 1, -1)
+    kk = k0 ** 2 + k1 ** 2 + k2 ** 2
+    invk = torch.where(kk > 0, 1.0 / kk.clamp_min(1e-30), torch.zeros_like(kk))
+    xk = torch.fft.fftn(x)
+    for b, kb in enumerate((k0, k1, k2)):
+        want = torch.fft.ifftn(xk * (1j * kb * invk))
+        got = torch.zeros(n, dtype=torch.complex128)
+        for r, o in enumerate(outs):
+            c = (r // p1, r % p1)
+            l0, l1 = n[0] // p0, n[1] // p1
+            got[c[0] * l0:(c[0] + 1) * l0, c[1] * l1:(c[1] + 1) * l1, :] = o[b]
+        torch.testing.assert_close(got, want, rtol=1e-10, atol=1e-12)
