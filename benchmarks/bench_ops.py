@@ -154,6 +154,18 @@ def main():
                     ms = timed(fn, args.warmup, args.iters, world, device)
                     emit(op=name, backend=backend, halo=h, ms=ms, egress_mib=face_bytes / 2 ** 20,
                          egress_gbs=face_bytes / ms / 1e6, note="functional variants include the copy of the padded block; the in-place one moves only the slabs")
+                if backend == "b200":
+                    # the same exchange on a peer-visible block: slabs stored straight into the neighbours' blocks
+                    pv = jd.empty_sharded(mesh, tuple(blk.shape), torch.float32)
+                    pv.local.copy_(blk)
+                    ms = timed(lambda: jd.halo_exchange_(pv, (h, h), (True, True), backend="b200"), args.warmup,
+                               args.iters, world, device)
+                    emit(op="halo_exchange_inplace_peer_visible", backend=backend, halo=h, ms=ms,
+                         egress_mib=face_bytes / 2 ** 20, egress_gbs=face_bytes / ms / 1e6,
+                         frac_of_link=(face_bytes / (NVLINK_GBS * 1e9) * 1e3) / ms,
+                         note="direct pushes into the neighbours' padded blocks: barrier, one kernel, barrier")
+                    del pv
+                    jd.free_peer_visible(mesh)
                 del blk, st
         if "lpt" in ops:
             from jaxdecomp_b200.models.lpt import LPTConfig, LPTModel, lpt_loss

@@ -19,6 +19,7 @@ from __future__ import annotations
 
 from .ops.fft import fftfreq3d, pfft3d, pifft3d, rfftfreq3d
 from .ops.halo import halo_accumulate, halo_exchange, halo_exchange_, halo_reduce, pad_halo, unpad_halo
+from .ops.peer import empty_peer_visible, empty_sharded, free_peer_visible
 from .ops.transpose import (
     transpose_shard,
     transposeXtoY,
@@ -106,5 +107,5 @@ __all__ = [
     "HaloCommBackend", "TransposeCommBackend", "TransposeType", "Decomposition",
     "Mesh", "make_mesh", "set_mesh", "current_mesh", "single_rank_mesh", "init_distributed",
     "ShardedTensor", "shard", "PartitionSpec", "P", "NamedSharding", "PencilInfo", "GridConfig",
-    "save_sharded", "load_sharded",
+    "save_sharded", "load_sharded", "empty_sharded", "empty_peer_visible", "free_peer_visible",
 ]

@@ -41,7 +41,11 @@ static void raise_on(int rc, const char* what) {
 }
 
 // regions: list of (lo0, hi0, lo1, hi1, peer, stage_off)
-static HaloDesc make_halo_desc(const std::vector<std::tuple<int, int, int, int, int, long long>>& regions, int S0, int S1,
+using Region6 = std::tuple<int, int, int, int, int, long long>;
+// direct pushes: (lo0, hi0, lo1, hi1, peer, dlo0, dlo1)
+using Region7 = std::tuple<int, int, int, int, int, int, int>;
+
+static HaloDesc make_halo_desc(const std::vector<Region6>& regions, int S0, int S1,
                                int S2, int B, int elem_bytes, int is_f64, int accumulate) {
   HaloDesc d;
   std::memset(&d, 0, sizeof(d));
@@ -180,6 +184,21 @@ PYBIND11_MODULE(_jdb200, m) {
         for (size_t i = 0; i < r.size(); ++i) s.group_ranks[i] = r[i];
       });
 
+  // A block of device memory that every rank of a group can address: the storage behind peer-visible
+  // tensors (ops/peer.py).  Creation, export/open and close are collective like the arena's.
+  py::class_<SymmetricArena>(m, "PeerBlock")
+      .def(py::init<size_t, int, int>(), py::arg("bytes"), py::arg("world"), py::arg("me"))
+      .def("export_handles", [](const SymmetricArena& a) { return py::bytes(a.export_handles()); })
+      .def("open_peers", [](SymmetricArena& a, const std::vector<py::bytes>& hs) {
+        std::vector<std::string> v;
+        for (const auto& h : hs) v.push_back((std::string)h);
+        a.open_peers(v);
+      })
+      .def("close_peers", &SymmetricArena::close_peers)
+      .def("close", &SymmetricArena::close, py::arg("free_own") = true)
+      .def("ptr", [](const SymmetricArena& a, int peer) { return (uintptr_t)a.data(peer); })
+      .def_property_readonly("bytes", &SymmetricArena::bytes);
+
   py::class_<Runtime>(m, "Runtime")
       .def(py::init<int, int>(), py::arg("world"), py::arg("me"))
       .def("create_arena", &Runtime::create_arena)
@@ -224,6 +243,22 @@ PYBIND11_MODULE(_jdb200, m) {
       .def("set_pipelining", &Runtime::set_pipelining)
       .def("pipelining", &Runtime::pipelining)
       .def("pipelined_sections", &Runtime::pipelined_sections)
+      .def("halo_direct", [](Runtime& r, const std::vector<Region7>& push, const std::vector<Region6>& zero, int S0, int S1,
+                             int S2, int B, int elem_bytes, const std::vector<uintptr_t>& blocks, uintptr_t stream) {
+        if ((int)blocks.size() != r.world()) throw py::value_error("halo_direct: one block pointer per rank");
+        std::vector<Region6> plain;
+        for (const auto& g : push)
+          plain.emplace_back(std::get<0>(g), std::get<1>(g), std::get<2>(g), std::get<3>(g), std::get<4>(g), 0LL);
+        HaloDesc dp = make_halo_desc(plain, S0, S1, S2, B, elem_bytes, 0, 0);
+        for (size_t i = 0; i < push.size(); ++i) {
+          dp.reg[i].dlo0 = std::get<5>(push[i]);
+          dp.reg[i].dlo1 = std::get<6>(push[i]);
+        }
+        HaloDesc dz = make_halo_desc(zero, S0, S1, S2, B, elem_bytes, 0, 0);
+        std::vector<void*> ptrs;
+        for (uintptr_t b : blocks) ptrs.push_back(P(b));
+        raise_on(r.halo_direct(dp, zero.empty() ? nullptr : &dz, ptrs.data(), P(stream)), "halo_direct");
+      })
       .def("barrier", [](Runtime& r, uintptr_t stream) { raise_on(r.barrier(P(stream)), "barrier"); })
       .def("barriers_issued", &Runtime::barriers_issued)
       .def("launches", &Runtime::launches)

@@ -42,10 +42,15 @@ __global__ void halo_pack_kernel(HaloDesc d, RegionIndex ri, int vec_per_row) {
     const int a = (int)(k % n0);
     const int b = (int)(k / n0);
     const long long src_idx = (((long long)b * d.S0 + (g.lo0 + a)) * d.S1 + (g.lo1 + j)) * vec_per_row + v;
-    const long long dst_idx = (i - ri.start[r]);
     const V* src = (const V*)d.src;
-    V* dst = (V*)d.stage[g.peer] + g.stage_off;
-    dst[dst_idx] = src[src_idx];
+    if (d.direct) {
+      // final position in the neighbour's block: no staging slab, no unpack
+      const long long dst_idx = (((long long)b * d.S0 + (g.dlo0 + a)) * d.S1 + (g.dlo1 + j)) * vec_per_row + v;
+      ((V*)d.stage[g.peer])[dst_idx] = src[src_idx];
+    } else {
+      V* dst = (V*)d.stage[g.peer] + g.stage_off;
+      dst[i - ri.start[r]] = src[src_idx];
+    }
   }
 }
 
@@ -144,6 +149,8 @@ static bool valid(const HaloDesc& d) {
     const HaloRegion& g = d.reg[r];
     if (g.lo0 < 0 || g.hi0 > d.S0 || g.lo1 < 0 || g.hi1 > d.S1 || g.lo0 > g.hi0 || g.lo1 > g.hi1) return false;
     if (g.peer >= JD_MAX_PEERS) return false;
+    if (d.direct && (g.dlo0 < 0 || g.dlo0 + (g.hi0 - g.lo0) > d.S0 || g.dlo1 < 0 || g.dlo1 + (g.hi1 - g.lo1) > d.S1))
+      return false;
   }
   return true;
 }

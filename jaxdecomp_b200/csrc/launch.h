@@ -51,6 +51,7 @@ struct HaloRegion {
   int32_t lo0, hi0, lo1, hi1;
   int32_t peer;         // index into HaloDesc::stage (destination or source), -1: none (zero fill / skip)
   long long stage_off;  // element offset of this region's slab inside the staging buffer
+  int32_t dlo0, dlo1;   // direct pushes: first row / column of the region this slab lands in on the peer
 };
 struct HaloDesc {
   int32_t S0, S1, S2, B;   // padded local block (B = batch)
@@ -58,12 +59,15 @@ struct HaloDesc {
   int32_t nregions;
   int32_t accumulate;      // unpack: 0 overwrite, 1 add
   int32_t is_f64;          // accumulate arithmetic: 1 = float64/complex128, 0 = float32/complex64
+  int32_t direct;          // pack only: 1 = stage[p] is peer p's *block* (same shape as this rank's) and every
+                           // slab is stored at its final place there, rows [dlo0..) x columns [dlo1..)
   HaloRegion reg[8];
   void* stage[JD_MAX_PEERS];  // staging buffers (peer-visible)
   const void* src;            // local block read by pack
   void* dst;                  // local block written by unpack
 };
-// pack: for every region copy src[region] -> stage[reg.peer] + stage_off (peer stores)
+// pack: for every region copy src[region] -> stage[reg.peer] + stage_off (peer stores), or, in direct mode,
+// straight into the neighbour's padded block
 int launch_halo_pack(const HaloDesc& d, void* stream);
 // unpack: for every region dst[region] (=|+=) stage[reg.peer] + stage_off (local loads); peer == -1 -> zero (overwrite mode)
 int launch_halo_unpack(const HaloDesc& d, void* stream);

@@ -399,6 +399,31 @@ int Runtime::peek_flag(int word, uint32_t* value) const {
   return JD_OK;
 }
 
+int Runtime::halo_direct(HaloDesc push, const HaloDesc* zero, void* const* block, void* stream) {
+  if (!arena_ && world_ > 1) {
+    set_last_error("runtime: direct halo exchange without arena (flags)");
+    return JD_ERR_INVALID_ARG;
+  }
+  int rc;
+  if (world_ > 1 && (rc = barrier(stream)) != JD_OK) return rc;
+  push.direct = 1;
+  push.src = block[me_];
+  push.dst = block[me_];
+  for (int p = 0; p < JD_MAX_PEERS; ++p) push.stage[p] = p < world_ ? block[p] : nullptr;
+  if ((rc = launch_halo_pack(push, stream)) != JD_OK) return rc;
+  ++launches_;
+  if (zero != nullptr) {
+    HaloDesc z = *zero;
+    z.src = block[me_];
+    z.dst = block[me_];
+    for (int p = 0; p < JD_MAX_PEERS; ++p) z.stage[p] = nullptr;
+    if ((rc = launch_halo_unpack(z, stream)) != JD_OK) return rc;
+    ++launches_;
+  }
+  if (world_ > 1 && (rc = barrier(stream)) != JD_OK) return rc;
+  return JD_OK;
+}
+
 StatusBlock Runtime::read_status() const {
   StatusBlock s{};
   if (status_) s = *status_->host();

@@ -95,6 +95,11 @@ class Runtime {
   // pack -> (zero fill) -> barrier -> unpack through arena slot 0; copies src to dst first when they differ
   int halo(HaloDesc pack, HaloDesc unpack, const HaloDesc* zero, const void* src, void* dst, long long bytes,
            void* stream);
+  // In-place exchange on blocks that are themselves peer visible (block[p]: the block of arena rank p,
+  // same shape on every rank): barrier (nobody still reads the halos that are about to be overwritten),
+  // one kernel that stores every slab at its final place in the neighbours' blocks (+ zero fill of halos
+  // without a source), barrier (everything has landed).  No staging slab, no unpack pass.
+  int halo_direct(HaloDesc push, const HaloDesc* zero, void* const* block, void* stream);
   long long barriers_issued() const { return host_epoch_; }
   long long launches() const { return launches_; }
 

@@ -284,6 +284,11 @@ class MeshRuntime:
             out = x
             if not regions:
                 return out
+            from . import peer as _peer
+
+            hit = _peer.lookup(self.mesh, x) if os.environ.get("JD_B200_HALO_DIRECT", "1") != "0" else None
+            if hit is not None:
+                return self._halo_direct(x, hit, (S0, S1, S2), B, regions, periods)
         else:
             out = torch.empty_like(x)
             if not regions:
@@ -302,6 +307,27 @@ class MeshRuntime:
         is_f64 = int(x.dtype in (torch.float64, torch.complex128))
         self.rt.halo(pack, unpack, [], S0, S1, S2, B, eb, is_f64, 0, x.data_ptr(), out.data_ptr(), _stream())
         return out
+
+    def _halo_direct(self, x, hit, shape, B, regions, periods):
+        """In-place exchange on a peer-visible block: every slab is stored at its final place in the
+        neighbour's block (which has the same shape and sits at the same offset of the neighbour's
+        allocation), between two barriers."""
+        alloc, offset = hit
+        S0, S1, S2 = shape
+        per = (bool(periods[0]), bool(periods[1]))
+        push, zero = [], []
+        for (d0, d1, send, recv) in regions:
+            dst = self.mesh.neighbor(d0, d1, per)
+            src = self.mesh.neighbor(-d0, -d1, per)
+            if dst is not None:
+                push.append((send[0][0], send[0][1], send[1][0], send[1][1], self._arena_rank(dst), recv[0][0], recv[1][0]))
+            if src is None:
+                zero.append((recv[0][0], recv[0][1], recv[1][0], recv[1][1], -1, 0))
+        self.ensure_arena(1)  # the flags of the barriers live in the arena
+        self.check_status()
+        blocks = [p + offset for p in alloc.ptrs]
+        self.rt.halo_direct(push, zero, S0, S1, S2, B, x.element_size(), blocks, _stream())
+        return x
 
     def halo_accumulate(self, g: torch.Tensor, extents, periods) -> torch.Tensor:
         g = _aligned(g)
@@ -364,7 +390,13 @@ def launches(mesh: Mesh) -> int:
 
 
 def finalize(collective: bool = True) -> None:
-    """Free every arena and forget all plans (collective when ranks > 1)."""
+    """Free every arena and peer-visible block and forget all plans (collective when ranks > 1)."""
+    try:
+        from . import peer as _peer
+
+        _peer.free_peer_visible(None, collective=collective)
+    except Exception:  # noqa: BLE001 - best effort at shutdown
+        pass
     for rt in list(_runtimes.values()):
         try:
             rt.release(collective=collective)
@@ -376,6 +408,12 @@ def finalize(collective: bool = True) -> None:
 @atexit.register
 def _at_exit():
     # at interpreter exit the process group may be gone: free without a host barrier
+    try:
+        from . import peer as _peer
+
+        _peer.free_peer_visible(None, collective=False)
+    except Exception:  # noqa: BLE001
+        pass
     for rt in list(_runtimes.values()):
         try:
             rt.release(collective=False)

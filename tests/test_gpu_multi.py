@@ -101,6 +101,23 @@ def _ops_worker(rank, world):
                 assert torch.equal(a.local, b.local), (pdims, periods)
                 c = jd.halo_exchange_(jd.ShardedTensor(blk.clone(), mesh), (2, 3), periods, backend="b200")
                 assert torch.equal(c.local, b.local), (pdims, periods)
+                # peer-visible block: slabs are stored straight into the neighbours' padded blocks
+                pv = jd.empty_sharded(mesh, (2, 12, 14, 10), dtype, spec=(None, "z", "y", None))
+                want = []
+                for i in range(2):
+                    pv.local[i].copy_(blk * (i + 1))
+                    want.append(jd.halo_exchange(jd.ShardedTensor(blk * (i + 1), mesh), (2, 3), periods, backend="torch").local)
+                rtm = b200_backend.get_runtime(mesh)
+                before = rtm.rt.launches()
+                jd.halo_exchange_(pv, (2, 3), periods, backend="b200")
+                assert torch.equal(pv.local, torch.stack(want)), (pdims, periods)
+                # two barriers and one push (plus one zero fill at a non-periodic edge): no staging, no unpack
+                assert rtm.rt.launches() - before <= 4
+                view = jd.ShardedTensor(pv.local[1], mesh)                # a slice of the block works too
+                view.local.copy_(blk)
+                jd.halo_exchange_(view, (2, 3), periods, backend="b200")
+                assert torch.equal(view.local, c.local), (pdims, periods)
+                jd.free_peer_visible(mesh)
                 a = jd.halo_accumulate(st, (2, 3), periods, backend="b200")
                 b = jd.halo_accumulate(st, (2, 3), periods, backend="torch")
                 torch.testing.assert_close(a.local, b.local, rtol=1e-6, atol=1e-6)
