@@ -9,8 +9,10 @@
 
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 
 #include "launch.h"
 #include "tile_ops.h"
@@ -28,11 +30,12 @@ static __device__ __align__(256) float2 g_static_scratch[JDB_STATIC_MAX_ELEMS];
 static __device__ __align__(256) float2 g_static_twiddle[3][kMaxAxis];
 
 struct DeviceSlots {
-  bool ready = false;
+  std::atomic<bool> ready{false};
   float2* scratch = nullptr;
   float2* twiddle = nullptr;
 };
 DeviceSlots g_slots[kMaxDevices];
+std::mutex g_setup_mutex;
 thread_local char g_error[256] = "";
 
 int fail(const char* msg) {
@@ -117,19 +120,37 @@ extern "C" int jdb_fft3d_c64_static(const void* in, void* out, int n0, int n1, i
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices)
     return fail("jdb_fft3d_c64_static: no current CUDA device");
-  DeviceSlots& sl = g_slots[dev];
-  if (!sl.ready) {
-    // once per device, with that device current: turn the symbols into device addresses
-    void* p = nullptr;
-    cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
-    if (e != cudaSuccess) return fail(cudaGetErrorString(e));
-    sl.scratch = static_cast<float2*>(p);
-    e = cudaGetSymbolAddress(&p, g_static_twiddle);
-    if (e != cudaSuccess) return fail(cudaGetErrorString(e));
-    sl.twiddle = static_cast<float2*>(p);
-    sl.ready = true;
+  {
+    // partially overlapping buffers would let pass 2 or 3 overwrite input that pass 1 has not read yet
+    const uintptr_t a = (uintptr_t)in, b = (uintptr_t)out, bytes = (uintptr_t)total * sizeof(float2);
+    if (a < b + bytes && b < a + bytes) return fail("jdb_fft3d_c64_static: in and out must not overlap");
   }
   cudaStream_t stream = (cudaStream_t)stream_;
+  DeviceSlots& sl = g_slots[dev];
+  // Set-up, once per device and with that device current: turn the symbols into device addresses.  The
+  // flag is read with acquire and written with release ordering, and the set-up itself runs under a
+  // mutex, so two host threads that make their first call at the same time both see complete slots.
+  if (!sl.ready.load(std::memory_order_acquire)) {
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess) {
+      cudaGetLastError();
+      return fail("jdb_fft3d_c64_static: cannot query the stream");
+    }
+    if (cap != cudaStreamCaptureStatusNone)
+      return fail("jdb_fft3d_c64_static: the first call on a device resolves symbol addresses and must be made "
+                  "outside of a stream capture");
+    std::lock_guard<std::mutex> lk(g_setup_mutex);
+    if (!sl.ready.load(std::memory_order_relaxed)) {
+      void* p = nullptr;
+      cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+      if (e != cudaSuccess) return fail(cudaGetErrorString(e));
+      sl.scratch = static_cast<float2*>(p);
+      e = cudaGetSymbolAddress(&p, g_static_twiddle);
+      if (e != cudaSuccess) return fail(cudaGetErrorString(e));
+      sl.twiddle = static_cast<float2*>(p);
+      sl.ready.store(true, std::memory_order_release);
+    }
+  }
   // lengths in the order the passes use them
   const int len[3] = {inverse ? n0 : n2, n1, inverse ? n2 : n0};
   for (int i = 0; i < 3; ++i) {

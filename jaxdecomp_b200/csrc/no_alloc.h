@@ -22,7 +22,10 @@
 //
 // Set-up: the first call on a device resolves the device addresses of the
 // static arrays (one cudaGetSymbolAddress per array, with that device
-// current).  Make that first call outside of any stream capture.
+// current).  Make that first call outside of any stream capture: a first call
+// on a capturing stream is refused with an error instead of disturbing the
+// capture.  Host threads may make their first calls concurrently (the set-up
+// is serialised and published with release/acquire ordering).
 //
 // Sharing: all calls on a device use the same static arrays, which keep the
 // contents of the previous call.  Nothing in them needs to start at zero (each
@@ -31,7 +34,7 @@
 // scratch and give wrong results.  Order them on one stream or with events.
 //
 // `in` and `out` are device pointers to n0*n1*n2 complex64 values, 16-byte
-// aligned, and must not alias.  `stream` is a cudaStream_t (0 for the default
+// aligned; the two ranges must not overlap, not even partially.  `stream` is a cudaStream_t (0 for the default
 // stream).  Returns 0 on success.
 #pragma once
 

@@ -75,3 +75,8 @@ def test_static_scratch_fft_rejects_what_does_not_fit():
     assert b"power of two" in lib.jdb_fft3d_c64_static_error()
     assert lib.jdb_fft3d_c64_static(a.data_ptr(), a.data_ptr(), 8, 8, 8, 0, None) != 0
     assert b"alias" in lib.jdb_fft3d_c64_static_error()
+    buf = torch.zeros(1024, device=dev, dtype=torch.complex64)
+    assert lib.jdb_fft3d_c64_static(buf.data_ptr(), buf[256:].data_ptr(), 8, 8, 8, 0, None) != 0   # half-overlapping ranges
+    assert b"overlap" in lib.jdb_fft3d_c64_static_error()
+    assert lib.jdb_fft3d_c64_static(buf.data_ptr(), buf[512:].data_ptr(), 8, 8, 8, 0, None) == 0   # adjacent ranges are fine
+    torch.cuda.synchronize()
