@@ -241,7 +241,7 @@ __device__ __forceinline__ void fast_stage(cx<R>* sm, cx<R>* rowp, int j, int sg
 }
 
 // One tile: rows [t0, t0 + T) of (o, b).
-template <typename Cfg, typename R>
+template <typename Cfg, typename R, bool MUL = false>
 __device__ __forceinline__ void fast_tile(const PassDesc& d, cx<R>* sm, int tile, int tiles_t, int tid) {
   using E = cx<R>;
   constexpr int UPR = Cfg::UPR;
@@ -262,9 +262,11 @@ __device__ __forceinline__ void fast_tile(const PassDesc& d, cx<R>* sm, int tile
 #pragma unroll
     for (int k = 0; k < 16; ++k) a[k] = src[k * UPR];
   }
-  if (d.mul_mode != JD_MUL_NONE) {
+  if constexpr (MUL) {
+    // fused Fourier-space multiplier (PassDesc::mul_mode), applied to the values as they arrive
+    const MulRow<R> mr(d, t0 + row, o, b);
 #pragma unroll
-    for (int k = 0; k < 16; ++k) a[k] = apply_mul(d, a[k], j + k * UPR, t0 + row, o, b);
+    for (int k = 0; k < 16; ++k) a[k] = mr.apply(a[k], j + k * UPR);
   }
   if (inv) {
 #pragma unroll
@@ -324,18 +326,22 @@ __device__ __noinline__ void fast_tile_call(const PassDesc& d, cx<R>* sm, int ti
   fast_tile<Cfg, R>(d, sm, tile, tiles_t, threadIdx.x);
 }
 
-// LOOP = false: one tile per block.  LOOP = true: the grid is smaller than the number of tiles
+// VARIANT 0: one tile per block.  VARIANT 1: the grid is smaller than the number of tiles
 // (PassDesc::grid_limit) and every block walks over several tiles, in launch order; such a pass leaves
-// the other SMs to a pass that runs at the same time on another stream.
-template <typename R, int LOGM, int LOGT, bool STORE_T, bool LOOP>
+// the other SMs to a pass that runs at the same time on another stream.  VARIANT 2: one tile per block with
+// the fused input multiplier (a variant of its own so that the plain kernels keep their register allocation).
+template <typename R, int LOGM, int LOGT, bool STORE_T, int VARIANT>
 __global__ void __launch_bounds__((FastCfg<R, LOGM, LOGT, STORE_T>::NT), (FastCfg<R, LOGM, LOGT, STORE_T>::MINB))
     fft_fast_kernel(const __grid_constant__ PassDesc d) {
   using Cfg = FastCfg<R, LOGM, LOGT, STORE_T>;
+  constexpr bool LOOP = VARIANT == 1;
   extern __shared__ __align__(16) unsigned char fast_smem[];
   cx<R>* sm = reinterpret_cast<cx<R>*>(fast_smem);
   if (pass_aborted(d)) return;
   const int tiles_t = d.Tn >> LOGT;
-  if constexpr (!LOOP) {
+  if constexpr (VARIANT == 2) {
+    fast_tile<Cfg, R, true>(d, sm, blockIdx.x, tiles_t, threadIdx.x);
+  } else if constexpr (!LOOP) {
     fast_tile<Cfg, R>(d, sm, blockIdx.x, tiles_t, threadIdx.x);
   } else {
     const int ntiles = tiles_t * d.On;
@@ -399,10 +405,13 @@ static int launch_fast_t(const PassDesc& d, cudaStream_t stream) {
     set_last_error("fast pass: grid too large");
     return JD_ERR_INVALID_ARG;
   }
-  const bool loop = d.grid_limit > 0 && d.grid_limit < nblocks;
-  auto kern = loop ? fft_fast_kernel<R, LOGM, LOGT, STORE_T, true> : fft_fast_kernel<R, LOGM, LOGT, STORE_T, false>;
-  static bool configured[2] = {false, false};
-  if (!configured[loop]) {
+  const bool mul = d.mul_mode != JD_MUL_NONE;
+  const bool loop = !mul && d.grid_limit > 0 && d.grid_limit < nblocks;
+  const int variant = mul ? 2 : (loop ? 1 : 0);
+  auto kern = mul ? fft_fast_kernel<R, LOGM, LOGT, STORE_T, 2>
+                  : (loop ? fft_fast_kernel<R, LOGM, LOGT, STORE_T, 1> : fft_fast_kernel<R, LOGM, LOGT, STORE_T, 0>);
+  static bool configured[3] = {false, false, false};
+  if (!configured[variant]) {
     if (Cfg::SMEM > 48 * 1024) {
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM);
       if (e != cudaSuccess) {
@@ -410,7 +419,7 @@ static int launch_fast_t(const PassDesc& d, cudaStream_t stream) {
         return JD_ERR_CUDA;
       }
     }
-    configured[loop] = true;
+    configured[variant] = true;
   }
   const long long grid = loop ? d.grid_limit : nblocks;
   kern<<<dim3((unsigned)grid, (unsigned)d.B, 1), Cfg::NT, Cfg::SMEM, stream>>>(d);
