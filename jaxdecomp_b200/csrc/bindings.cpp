@@ -92,7 +92,7 @@ PYBIND11_MODULE(_jdb200, m) {
 #define RW(f) .def_readwrite(#f, &PassDesc::f)
       RW(is_c) RW(is_t) RW(is_o) RW(is_b) RW(os_c) RW(os_t) RW(os_o) RW(os_b) RW(out_base) RW(C) RW(Tn) RW(On) RW(B)
       RW(Cl) RW(Tl) RW(Ol) RW(npeers) RW(fft_mode) RW(M) RW(inverse) RW(T) RW(Cc) RW(pitch) RW(elem_bytes)
-      RW(load_t_contig) RW(store_t_contig) RW(use_bulk) RW(mul_mode) RW(vec_in) RW(vec_out) RW(intra_pad) RW(logT) RW(logW) RW(split_axis) RW(scale) RW(grid_limit) RW(out_limit) RW(in_pair) RW(out_pair)
+      RW(load_t_contig) RW(store_t_contig) RW(use_bulk) RW(mul_mode) RW(vec_in) RW(vec_out) RW(intra_pad) RW(logT) RW(logW) RW(split_axis) RW(scale) RW(grid_limit) RW(out_limit)
 #undef RW
       .def_property("in_ptr", [](const PassDesc& d) { return (uintptr_t)d.in; },
                     [](PassDesc& d, uintptr_t v) { d.in = P(v); })

@@ -183,12 +183,8 @@ int validate_pass(const PassDesc& d) {
     }
     if (seen != 7) return JD_ERR_INVALID_ARG;
   }
-  if (d.in_pair && (d.in_pair > 2 || d.load_t_contig || d.vec_in || d.use_bulk || ((d.in_pair == 1 ? d.On : d.Tn) & 1) ||
-                    d.fft_mode == JD_FFT_MIXED))
-    return JD_ERR_INVALID_ARG;
-  if (d.out_pair && (!d.store_t_contig || d.vec_out || (d.Cl & 1) || d.fft_mode == JD_FFT_MIXED)) return JD_ERR_INVALID_ARG;
-  if (d.load_t_contig ? d.is_t != 1 : d.is_c != (d.in_pair ? 2 : 1)) return JD_ERR_INVALID_ARG;
-  if (d.store_t_contig ? d.os_t != (d.out_pair ? 2 : 1) : d.os_c != 1) return JD_ERR_INVALID_ARG;
+  if (d.load_t_contig ? d.is_t != 1 : d.is_c != 1) return JD_ERR_INVALID_ARG;
+  if (d.store_t_contig ? d.os_t != 1 : d.os_c != 1) return JD_ERR_INVALID_ARG;
   if (d.fft_mode == JD_COPY) {
     if (d.Cc < 1 || d.pitch < d.Cc) return JD_ERR_INVALID_ARG;
   } else {

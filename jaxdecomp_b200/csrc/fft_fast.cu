@@ -258,15 +258,9 @@ __device__ __forceinline__ void fast_tile(const PassDesc& d, cx<R>* sm, int tile
   E a[16];
   {
     const E* __restrict__ src =
-        (const E*)d.in + (in_o_offset(d, o) + (long long)b * d.is_b + in_t_offset(d, t0 + row));
-    if (d.in_pair) {
-      // pair-blocked input: this row's elements alternate with those of the neighbouring plane
+        (const E*)d.in + ((long long)o * d.is_o + (long long)b * d.is_b + (long long)(t0 + row) * d.is_t + j);
 #pragma unroll
-      for (int k = 0; k < 16; ++k) a[k] = src[2 * (j + k * UPR)];
-    } else {
-#pragma unroll
-      for (int k = 0; k < 16; ++k) a[k] = src[j + k * UPR];
-    }
+    for (int k = 0; k < 16; ++k) a[k] = src[k * UPR];
   }
   if constexpr (MUL) {
     // fused Fourier-space multiplier (PassDesc::mul_mode), applied to the values as they arrive
@@ -319,7 +313,7 @@ __device__ __forceinline__ void fast_tile(const PassDesc& d, cx<R>* sm, int tile
       E v = a[k];
       if (inv) v = cswap(v);
       if (do_scale) v = cscale(v, scale);
-      store_elem<E>(d, ob.peer + pc + pt, toff + out_c_offset(d, cl), v);
+      store_elem<E>(d, ob.peer + pc + pt, toff + (long long)cl * d.os_c, v);
     }
   }
 }
@@ -388,14 +382,14 @@ bool fast_pass_eligible(const PassDesc& d) {
   if (d.fft_mode != JD_FFT_POW2 || d.tw_stage == nullptr) return false;
   if (d.elem_bytes != 8 && d.elem_bytes != 16) return false;
   if (d.M < (d.elem_bytes == 8 ? 128 : 256) || d.M > (d.elem_bytes == 8 ? 4096 : 2048) || d.C != d.M) return false;
-  if (d.load_t_contig || d.is_c != (d.in_pair ? 2 : 1)) return false;
+  if (d.load_t_contig || d.is_c != 1) return false;
   int logM = 0;
   while ((1 << logM) < d.M) ++logM;
   // the small tile height must divide the rows (the big variant is used only when it divides too)
   const int lt = fast_pass_logT(logM, d.elem_bytes, false);
   if (d.Tn % (1 << lt)) return false;
   if (d.store_t_contig) {
-    if (d.os_t != (d.out_pair ? 2 : 1)) return false;
+    if (d.os_t != 1) return false;
     if (d.split_axis == 1 && !is_pow2(d.Cl)) return false;
   } else {
     if (d.os_c != 1) return false;

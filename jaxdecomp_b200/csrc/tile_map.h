@@ -80,17 +80,6 @@ struct PassDesc {
   int32_t logT;           // T == 1 << logT
   int32_t logW;           // columns held per row (M in fft modes, Cc in copy mode) == 1 << logW
   int32_t split_axis;     // which axis selects the peer: 0 none, 1 c, 2 t, 3 o
-  // Pair-blocked intermediate layout between a rotating pass and the pass that reads its result: the
-  // writer's columns c are interleaved in pairs, (c, t, o) -> (c>>1)*2*os_c + (t*os_t + o*os_o) + (c&1) with
-  // os_t == 2, so that the T rows of two neighbouring columns form one run of 2*T elements (128 bytes for
-  // eight complex64 rows, where the plain rotated layout gives 64-byte runs that reach only half of the
-  // write bandwidth).  The reader sees the same array with its o axis paired:
-  // (c, t, o) -> (o>>1)*2*is_o + (o&1) + t*is_t + c*2 (is_c == 2) -- or, when the writer's columns are the
-  // reader's t axis, with the roles of t and o exchanged.  Strides of axes that lie inside a column of the
-  // writer are doubled by the planner, the others are left alone.  Only layouts between two passes of one
-  // plan are blocked; what a caller sees never is.
-  int32_t out_pair;       // 1: store in the pair-blocked layout (os_t == 2)
-  int32_t in_pair;        // load from the pair-blocked layout (is_c == 2): 1 pairs along o, 2 pairs along t
   int32_t grid_limit;     // > 0: launch at most this many blocks, each looping over tiles (leaves the other
                           // SMs to a pass that runs concurrently on another stream); 0: one block per tile
   double scale;
@@ -112,10 +101,8 @@ struct PassDesc {
 JD_HD void out_location(const PassDesc& d, int c, int t, int o, int b, int& peer, long long& off) {
   const int pc = c / d.Cl, pt = t / d.Tl, po = o / d.Ol;
   peer = pc + pt + po;
-  const int cl = c - pc * d.Cl;
-  const long long cpart = d.out_pair ? (long long)(cl >> 1) * 2 * d.os_c + (cl & 1) : (long long)cl * d.os_c;
-  off = d.out_base + cpart + (long long)(t - pt * d.Tl) * d.os_t + (long long)(o - po * d.Ol) * d.os_o +
-        (long long)b * d.os_b;
+  off = d.out_base + (long long)(c - pc * d.Cl) * d.os_c + (long long)(t - pt * d.Tl) * d.os_t +
+        (long long)(o - po * d.Ol) * d.os_o + (long long)b * d.os_b;
 }
 
 // Restrict a pass to the rows [lo, lo + len) of its t axis (role == 2) or its o axis (role == 3).
@@ -130,7 +117,6 @@ inline bool restrict_pass(PassDesc& d, int role, int lo, int len) {
   if (d.split_axis == role || lo < 0 || len <= 0) return false;
   const int ext = role == 2 ? d.Tn : d.On;
   if (lo + len > ext) return false;
-  if (role == 3 && d.in_pair == 1 && ((lo | len) & 1)) return false;  // pairs must stay together
   if (role == 2) {
     // tile heights are powers of two up to 32 (the specialised kernels pick theirs from Tn's divisibility)
     const int align = d.T > 32 ? d.T : 32;
@@ -149,9 +135,7 @@ inline bool restrict_pass(PassDesc& d, int role, int lo, int len) {
 }
 
 JD_HD long long in_location(const PassDesc& d, int c, int t, int o, int b) {
-  const long long opart = d.in_pair == 1 ? (long long)(o >> 1) * 2 * d.is_o + (o & 1) : (long long)o * d.is_o;
-  const long long tpart = d.in_pair == 2 ? (long long)(t >> 1) * 2 * d.is_t + (t & 1) : (long long)t * d.is_t;
-  return (long long)c * d.is_c + tpart + opart + (long long)b * d.is_b;
+  return (long long)c * d.is_c + (long long)t * d.is_t + (long long)o * d.is_o + (long long)b * d.is_b;
 }
 
 }  // namespace jdb

@@ -201,24 +201,11 @@ JD_HD E prepare_value(const PassDesc& d, E v, int c, int t, int o, int b) {
   return v;
 }
 
-// offset of plane o of the input (pair-blocked layouts interleave neighbouring planes)
-JD_HD long long in_o_offset(const PassDesc& d, int o) {
-  return d.in_pair == 1 ? (long long)(o >> 1) * 2 * d.is_o + (o & 1) : (long long)o * d.is_o;
-}
-// offset of row t of the input (the other pairing: neighbouring rows interleaved)
-JD_HD long long in_t_offset(const PassDesc& d, int t) {
-  return d.in_pair == 2 ? (long long)(t >> 1) * 2 * d.is_t + (t & 1) : (long long)t * d.is_t;
-}
-// offset of local column cl of the output (pair-blocked layouts interleave neighbouring columns)
-JD_HD long long out_c_offset(const PassDesc& d, int cl) {
-  return d.out_pair ? (long long)(cl >> 1) * 2 * d.os_c + (cl & 1) : (long long)cl * d.os_c;
-}
-
 // ---- load ---------------------------------------------------------------------------------
 // Rows t >= Tn (ragged last tile) and columns >= C are filled with zeros.
 template <typename E>
 JD_HD void tile_load(const PassDesc& d, E* tile, int o, int t0, int c0, int b, int tid, int nt) {
-  const E* in = (const E*)d.in + (in_o_offset(d, o) + (long long)b * d.is_b);
+  const E* in = (const E*)d.in + ((long long)o * d.is_o + (long long)b * d.is_b);
   const int T = d.T, logT = d.logT, logW = d.logW, W = 1 << logW;
   const int cols = tile_cols(d, c0);
   const int pad = d.intra_pad;
@@ -275,7 +262,7 @@ JD_HD void tile_load(const PassDesc& d, E* tile, int o, int t0, int c0, int b, i
         if (c >= wlim) continue;
         E v = zero;
         if (c < cols && t0 + t < d.Tn)
-          v = prepare_value(d, in[in_t_offset(d, t0 + t) + (long long)(c0 + c) * d.is_c], c0 + c, t0 + t, o, b);
+          v = prepare_value(d, in[(long long)(t0 + t) * d.is_t + (long long)(c0 + c) * d.is_c], c0 + c, t0 + t, o, b);
         tile[t * d.pitch + padidx(c, pad)] = v;
       }
     }
@@ -343,7 +330,7 @@ JD_HD long long out_offset(const PassDesc& d, const OutBase& ob, int c, int t, i
   const int pc = d.split_axis == 1 ? c / d.Cl : 0;
   const int pt = d.split_axis == 2 ? t / d.Tl : 0;
   peer = ob.peer + pc + pt;
-  return ob.off + out_c_offset(d, c - pc * d.Cl) + (long long)(t - pt * d.Tl) * d.os_t;
+  return ob.off + (long long)(c - pc * d.Cl) * d.os_c + (long long)(t - pt * d.Tl) * d.os_t;
 }
 
 template <typename E>
@@ -370,7 +357,7 @@ JD_HD void tile_store(const PassDesc& d, const E* tile, int o, int t0, int c0, i
         int cl = c0 + c - pc * d.Cl;
         const E* src = tile + t * d.pitch;
         for (; c < cols; c += step) {
-          const long long doff = toff + out_c_offset(d, cl);
+          const long long doff = toff + (long long)cl * d.os_c;
           const int col = padidx(c, pad);
           if (vec) {
             pair_of<E> p;

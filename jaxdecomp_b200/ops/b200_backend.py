@@ -35,7 +35,7 @@ _runtimes: Dict[tuple, "MeshRuntime"] = {}
 _default_slot_bytes = 0
 # switches that change how a plan is tiled: part of the plan key
 _TUNING_ENV = ("JD_B200_TILE_T", "JD_B200_BULK", "JD_B200_INTRAPAD", "JD_B200_ROWPAD", "JD_B200_FAST",
-               "JD_B200_PIPE_MIN_BYTES", "JD_B200_BLOCKED")
+               "JD_B200_PIPE_MIN_BYTES")
 # exchange passes smaller than this (bytes per rank) are not pipelined: below it the extra launches and
 # per-chunk barriers cost more than the overlap gains
 _PIPE_MIN_BYTES = 256 << 20
@@ -143,7 +143,6 @@ class MeshRuntime:
         tail_plain_from = n
         while tail_plain_from > 0 and specs[tail_plain_from - 1].plain:
             tail_plain_from -= 1
-        blocked = _passes.blocked_pairs(specs, eb)
         bytes_per = specs[0].numel * eb * nbatch
         plan_steps = []
         slot_bytes = 0
@@ -161,15 +160,10 @@ class MeshRuntime:
                           [2.0 * 3.141592653589793 / float(b) for b in box])
                 d.is_b = 0
                 d.use_bulk = 0
-            if i in blocked:
-                _passes.mark_blocked(d, writer=True)
-            if i - 1 in blocked:
-                _passes.mark_blocked(d, writer=False, pairing=blocked[i - 1])
             st = nat.PlanStep()
             st.in_kind = cur_kind
             last = i == n - 1
-            # the writer of a blocked layout needs a buffer of its own: its reader cannot run in place
-            if not remote and (last or i + 1 >= tail_plain_from) and i not in blocked:
+            if not remote and (last or i + 1 >= tail_plain_from):
                 out_kind = nat.BUF_USER_OUT
             else:
                 out_kind = next_slot

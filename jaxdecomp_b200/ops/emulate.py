@@ -75,7 +75,6 @@ def emulate_steps(blocks: List[torch.Tensor], steps: Sequence[Step], pdims: Sequ
         compiled.append(ps)
     npass = len(compiled[0])
     last_fft = max((i for i, p in enumerate(compiled[0]) if p.fft), default=-1)
-    blocked = _passes.blocked_pairs(compiled[0], eb)
     cur = [b.contiguous() for b in blocks]
 
     def alloc(i):
@@ -88,10 +87,6 @@ def emulate_steps(blocks: List[torch.Tensor], steps: Sequence[Step], pdims: Sequ
         d = _passes.fill_desc(nat, sp, eb, inverse, scale if i == last_fft else 1.0, nbatch,
                               remote=sp.npeers > 1, device_tables=False)
         d.use_bulk = 0
-        if i in blocked:
-            _passes.mark_blocked(d, writer=True)
-        if i - 1 in blocked:
-            _passes.mark_blocked(d, writer=False, pairing=blocked[i - 1])
         if fused_mul is not None and i == 0:
             n_orig, offs, box = fused_mul
             rot = (1, 2, 0)

@@ -208,57 +208,6 @@ def pipeline_cut(prod: PassSpec, cons: PassSpec, want_chunks: int) -> Optional[T
     return None
 
 
-# ---- pair-blocked layouts between two passes of a plan ----------------------------------------------------------
-
-def blocked_pairs(specs: Sequence[PassSpec], elem_bytes: int) -> dict:
-    """Local rotating passes whose result the next pass reads, and which therefore may write the
-    pair-blocked layout (``csrc/tile_map.h``: neighbouring columns interleaved, so that the stored runs
-    are twice as long).  Returns ``{i: pairing}`` for the writer ``i``: ``pairing`` says along which axis
-    of the reader ``i + 1`` the pairs run (1: its o axis, 2: its t axis).  Only buffers between two
-    passes of one plan are concerned.  ``JD_B200_BLOCKED=0`` switches it off."""
-    out = {}
-    if os.environ.get("JD_B200_BLOCKED", "1") == "0" or elem_bytes not in (8, 16):
-        return out
-    for i in range(len(specs) - 1):
-        a, b = specs[i], specs[i + 1]
-        if not (a.fft and b.fft) or a.npeers != 1 or tuple(a.out_shape) != tuple(b.in_shape):
-            continue
-        if not (_is_pow2(a.ext[0]) and a.ext[0] >= 8 and _is_pow2(b.ext[0]) and b.ext[0] >= 8):
-            continue  # the mixed-radix kernels read and write plain layouts only
-        ic, it, io = b.in_strides
-        oc, ot, oo = a.out_strides
-        # writer rotating (its t axis fastest), reader along that same, contiguous axis
-        if ot != 1 or oc == 1 or ic != 1 or a.ext[0] % 2:
-            continue
-        if io == oc and it == oo and b.ext[2] == a.ext[0]:
-            out[i] = 1      # the writer's columns are the reader's planes
-        elif it == oc and io == oo and b.ext[1] == a.ext[0] and b.ext[1] % 32 == 0:
-            out[i] = 2      # the writer's columns are the reader's rows (whole tiles of rows stay together)
-    return out
-
-
-def mark_blocked(d, writer: bool, pairing: int = 1) -> None:
-    """Switch a native descriptor to the pair-blocked layout on its output (writer) or input side.
-    Strides of axes that lie inside one column of the writer double; the others stay."""
-    if writer:
-        d.out_pair = 1
-        d.os_t = 2
-        if d.os_o < d.os_c:
-            d.os_o = 2 * d.os_o
-        d.vec_out = 0
-    else:
-        d.in_pair = pairing
-        d.is_c = 2
-        if pairing == 1:
-            if d.is_t < d.is_o:
-                d.is_t = 2 * d.is_t
-        else:
-            if d.is_o < d.is_t:
-                d.is_o = 2 * d.is_o
-        d.vec_in = 0
-        d.use_bulk = 0
-
-
 # ---- dtype-dependent tiling ----------------------------------------------------------------------------------
 
 def _env_int(name: str) -> Optional[int]:

@@ -193,28 +193,3 @@ def test_fused_displacement_multiplier_in_the_first_inverse_pass(pdims):
             l0, l1 = n[0] // p0, n[1] // p1
             got[c[0] * l0:(c[0] + 1) * l0, c[1] * l1:(c[1] + 1) * l1, :] = o[b]
         torch.testing.assert_close(got, want, rtol=1e-10, atol=1e-12)
-
-
-@pytest.mark.parametrize("pdims,expect_fwd,expect_inv", [((1, 1), {0: 1, 1: 1}, {0: 1, 1: 2}), ((1, 4), {1: 1}, {0: 1}),
-                                                         ((2, 2), {}, {})])
-def test_pair_blocked_layouts_between_local_passes(pdims, expect_fwd, expect_inv, monkeypatch):
-    """Local rotating passes hand their result to the next pass in the pair-blocked layout (twice as long
-    stored runs); the transform is bit-identical to the one through plain layouts."""
-    shape = (64, 64, 128)
-    x = torch.randn(shape, dtype=torch.complex64, generator=torch.Generator().manual_seed(11))
-    pt = pencil_type_from_pdims(pdims)
-    fwd = plan.fft_steps(pt, False, True, native=True)
-    inv = plan.fft_steps(pt, True, True, native=True)
-    blocks = emulate.split_blocks(x, pdims)
-    specs, kshape = passes.compile_passes(fwd, blocks[0].shape, pdims, (0, 0))
-    assert passes.blocked_pairs(specs, 8) == expect_fwd
-    ispecs, _ = passes.compile_passes(inv, kshape, pdims, (0, 0))
-    assert passes.blocked_pairs(ispecs, 8) == expect_inv
-    k_blocked = emulate.emulate_steps(blocks, fwd, pdims)
-    b_blocked = emulate.emulate_steps(k_blocked, inv, pdims, True, 1.0 / x.numel(), pipeline_chunks=4)
-    monkeypatch.setenv("JD_B200_BLOCKED", "0")
-    assert passes.blocked_pairs(specs, 8) == {}
-    k_plain = emulate.emulate_steps(blocks, fwd, pdims)
-    b_plain = emulate.emulate_steps(k_plain, inv, pdims, True, 1.0 / x.numel())
-    for a, b in zip(k_blocked + b_blocked, k_plain + b_plain):
-        assert torch.equal(a, b)
