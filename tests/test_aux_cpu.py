@@ -158,3 +158,73 @@ def test_spectral_poisson_example_runs():
                        capture_output=True, text=True, timeout=300, env=env)
     assert r.returncode == 0, r.stderr[-2000:]
     assert "max abs error" in r.stdout
+
+
+def test_reference_arm_runs_the_reference_api_when_it_can_be_imported(tmp_path):
+    """bench.py --impl reference must drive jaxdecomp.fft.pfft3d / pifft3d under jax.jit the way the reference's
+    own benchmark does and print the benchmark's JSON line; without jax it prints `unavailable`.  Here `jax` and
+    `jaxdecomp` are numpy stand-ins with just the API surface the runner touches, so that the code path runs."""
+    import json
+    import os
+    import subprocess
+    import sys
+    import textwrap
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    stub = tmp_path / "stubs"
+    (stub / "jax" / "experimental").mkdir(parents=True)
+    (stub / "jaxdecomp").mkdir()
+    (stub / "jax" / "__init__.py").write_text(textwrap.dedent("""
+        import numpy as _np
+        __version__ = "0.0-stub"
+        class _Arr(_np.ndarray):
+            def block_until_ready(self): return self
+            def addressable_data(self, i): return _np.asarray(self)
+        def _wrap(a): return _np.asarray(a).view(_Arr)
+        def jit(f): return lambda *a, **k: _wrap(f(*a, **k))
+        def make_mesh(shape, names): return ("mesh", tuple(shape), tuple(names))
+        class config:
+            @staticmethod
+            def update(k, v): pass
+        class distributed:
+            @staticmethod
+            def initialize(**kw): raise RuntimeError("single process stub")
+        from . import numpy, sharding  # noqa
+    """))
+    (stub / "jax" / "numpy.py").write_text("from numpy import *\n")
+    (stub / "jax" / "sharding.py").write_text(textwrap.dedent("""
+        class PartitionSpec(tuple):
+            def __new__(cls, *a): return tuple.__new__(cls, a)
+        class NamedSharding:
+            def __init__(self, mesh, spec): self.mesh, self.spec = mesh, spec
+    """))
+    (stub / "jax" / "experimental" / "__init__.py").write_text("")
+    (stub / "jax" / "experimental" / "multihost_utils.py").write_text(textwrap.dedent("""
+        import numpy as np, jax
+        def host_local_array_to_global_array(a, mesh, spec): return jax._wrap(a)
+        def sync_global_devices(name): pass
+        def process_allgather(a): return np.asarray(a)[None]
+    """))
+    (stub / "jaxdecomp" / "__init__.py").write_text("__version__ = '0.3.1-stub'\nfrom . import fft\n")
+    (stub / "jaxdecomp" / "fft.py").write_text(textwrap.dedent("""
+        import numpy as np
+        def pfft3d(a, norm="backward", backend="jax"): return np.fft.fftn(np.asarray(a)).transpose(1, 2, 0)
+        def pifft3d(a, norm="backward", backend="jax"): return np.fft.ifftn(np.asarray(a).transpose(2, 0, 1))
+    """))
+    env = dict(os.environ, PYTHONPATH=str(stub) + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+        env.pop(k, None)
+    r = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference", "--gpus", "1", "--steps", "2",
+                        "--warmup", "1", "--size", "16"], env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr
+    line = json.loads(r.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and "unavailable" not in line
+    assert line["value"] > 0 and line["n_gpus"] == 1 and line["steps"] == 2 and line["warmup"] == 3
+    assert line["config"]["roundtrip_max_rel_err"] < 1e-5
+    assert line["e2e"]["h2d_bytes_per_step"] == 16 ** 3 * 8 == line["e2e"]["d2h_bytes_per_step"]
+    # and without the reference on the path: one `unavailable` line, exit status 0
+    env2 = {k: v for k, v in env.items() if k != "PYTHONPATH"}
+    r2 = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference"], env=env2,
+                        capture_output=True, text=True, timeout=300)
+    assert r2.returncode == 0 and json.loads(r2.stdout.strip().splitlines()[-1])["impl"] == "reference"
+    assert "unavailable" in json.loads(r2.stdout.strip().splitlines()[-1])
