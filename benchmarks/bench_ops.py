@@ -141,6 +141,21 @@ def main():
                 egress = local_bytes * (p - 1) / p
                 emit(op=name, backend=backend, ms=ms, egress_gbs=egress / ms / 1e6 if egress else None,
                      local_gbs=2 * local_bytes / ms / 1e6)
+            if backend == "b200" and world > 1:
+                # result in a peer-visible block: the exchange stores straight into the other ranks' results
+                for name, src, p in (("transposeXtoY", x, p1), ("transposeYtoZ", y, p0), ("transposeZtoY", z, p0),
+                                     ("transposeYtoX", y, p1)):
+                    fn = getattr(jd, name)
+                    want = fn(src, backend=backend)
+                    pv = jd.empty_sharded(mesh, tuple(want.local.shape), want.local.dtype, spec=want.spec)
+                    ms = timed(lambda: fn(src, backend=backend, out=pv), args.warmup, args.iters, world, device)
+                    same = bool(torch.equal(pv.local, want.local))
+                    egress = local_bytes * (p - 1) / p
+                    emit(op=name + "_peer_visible_out", backend=backend, ms=ms, equal_to_plain=same,
+                         egress_gbs=egress / ms / 1e6 if egress else None,
+                         frac_of_link=(egress / ms / 1e6) / NVLINK_GBS if egress else None)
+                    del want, pv
+                    jd.free_peer_visible(mesh)
             del y, z
         if "halo" in ops:
             for h in (int(v) for v in args.halo.split(",")):

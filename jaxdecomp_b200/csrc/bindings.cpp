@@ -76,6 +76,7 @@ PYBIND11_MODULE(_jdb200, m) {
   m.attr("BUF_USER_OUT") = (int)BUF_USER_OUT;
   m.attr("BUF_SLOT_A") = (int)BUF_SLOT_A;
   m.attr("BUF_SLOT_B") = (int)BUF_SLOT_B;
+  m.attr("BUF_PEER_OUT") = (int)BUF_PEER_OUT;
   m.attr("FLAG_EPOCH_COUNTER_WORD") = kFlagEpochCounterWord;
   m.attr("FLAG_ABORT_WORD") = kFlagAbortWord;
   m.attr("BOUNDS_CHECK_BUILD") = (bool)JD_BOUNDS_CHECK_BUILD;
@@ -229,6 +230,14 @@ PYBIND11_MODULE(_jdb200, m) {
       .def("clear_plans", &Runtime::clear_plans)
       .def("execute", [](Runtime& r, int id, uintptr_t in, uintptr_t out, uintptr_t stream) {
         raise_on(r.execute(id, P(in), P(out), P(stream)), "execute");
+      })
+      .def("execute_peer_out", [](Runtime& r, int id, uintptr_t in, const std::vector<uintptr_t>& outs, uintptr_t stream) {
+        // outs: the result block's address on every arena rank (the plan's exchange stores into them)
+        if ((int)outs.size() != r.world() || r.world() > JD_MAX_PEERS)
+          throw std::invalid_argument("execute_peer_out: one result address per rank expected");
+        void* blocks[JD_MAX_PEERS] = {nullptr};
+        for (size_t p = 0; p < outs.size(); ++p) blocks[p] = P(outs[p]);
+        raise_on(r.execute(id, P(in), blocks[r.me()], P(stream), blocks), "execute_peer_out");
       })
       .def("halo", [](Runtime& r, const std::vector<std::tuple<int, int, int, int, int, long long>>& pack,
                       const std::vector<std::tuple<int, int, int, int, int, long long>>& unpack,

@@ -121,7 +121,7 @@ int Runtime::barrier(void* stream) {
 // peers, before another barrier has passed.
 int Runtime::sync_before(const PlanStep& st, void* stream) {
   if (world_ <= 1) return JD_OK;
-  const int is = st.in_kind - BUF_SLOT_A, os = st.out_kind - BUF_SLOT_A;
+  const int is = slot_of(st.in_kind), os = slot_of(st.out_kind);
   // read-after-remote-write: everybody's stores into the slot must have landed
   if (is >= 0 && slot_written_[is] == host_epoch_) {
     int rc = barrier(stream);
@@ -136,9 +136,16 @@ int Runtime::sync_before(const PlanStep& st, void* stream) {
 }
 
 void Runtime::fill_pointers(const PlanStep& st, PassDesc& d, const void* in, void* out) const {
-  const int is = st.in_kind - BUF_SLOT_A, os = st.out_kind - BUF_SLOT_A;
-  d.in = st.in_kind == BUF_USER_IN ? in : (st.in_kind == BUF_USER_OUT ? out : slot_ptr(is, me_));
-  for (int p = 0; p < d.npeers; ++p) d.out[p] = st.out_kind == BUF_USER_OUT ? out : slot_ptr(os, st.group_ranks[p]);
+  const int is = slot_of(st.in_kind), os = slot_of(st.out_kind);
+  d.in = st.in_kind == BUF_USER_IN ? in : ((st.in_kind == BUF_USER_OUT || st.in_kind == BUF_PEER_OUT) ? out : slot_ptr(is, me_));
+  for (int p = 0; p < d.npeers; ++p) {
+    if (st.out_kind == BUF_USER_OUT)
+      d.out[p] = out;
+    else if (st.out_kind == BUF_PEER_OUT)
+      d.out[p] = cur_peer_out_[st.group_ranks[p]];
+    else
+      d.out[p] = slot_ptr(os, st.group_ranks[p]);
+  }
   d.abort_word = (arena_ && world_ > 1) ? flag_ptr(me_) + kFlagAbortWord : nullptr;
   d.status = status_device();
 }
@@ -148,10 +155,10 @@ void Runtime::fill_pointers(const PlanStep& st, PassDesc& d, const void* in, voi
 int Runtime::launch_step(const Plan& pl, int plan_id, size_t index, const PassDesc* chunk_desc, const void* in,
                          void* out, void* stream) {
   const PlanStep& st = pl.steps[index];
-  const int is = st.in_kind - BUF_SLOT_A, os = st.out_kind - BUF_SLOT_A;
+  const int is = slot_of(st.in_kind), os = slot_of(st.out_kind);
   if (st.copy_only) {
-    const void* src = st.in_kind == BUF_USER_IN ? in : (st.in_kind == BUF_USER_OUT ? out : slot_ptr(is, me_));
-    void* dst = st.out_kind == BUF_USER_OUT ? out : slot_ptr(os, me_);
+    const void* src = st.in_kind == BUF_USER_IN ? in : ((st.in_kind == BUF_USER_OUT || st.in_kind == BUF_PEER_OUT) ? out : slot_ptr(is, me_));
+    void* dst = (st.out_kind == BUF_USER_OUT || st.out_kind == BUF_PEER_OUT) ? out : slot_ptr(os, me_);
     cudaError_t e = cudaMemcpyAsync(dst, src, (size_t)st.copy_bytes, cudaMemcpyDeviceToDevice, (cudaStream_t)stream);
     if (e != cudaSuccess) {
       set_last_error(cudaGetErrorString(e));
@@ -222,7 +229,7 @@ int Runtime::run_pipelined(Plan& pl, int plan_id, size_t index, const void* in, 
   if (rc != JD_OK) return rc;
   // hazards of both steps are settled up front, on the caller's stream
   if ((rc = sync_before(prod, stream)) != JD_OK) return rc;
-  const int cos = cons.out_kind - BUF_SLOT_A;
+  const int cos = slot_of(cons.out_kind);
   if (cos >= 0 && slot_read_[cos] == host_epoch_ && (rc = barrier(stream)) != JD_OK) return rc;
 
   PassDesc pd = prod.desc, cd = cons.desc;
@@ -286,7 +293,7 @@ int Runtime::run_pipelined(Plan& pl, int plan_id, size_t index, const void* in, 
   if (first_err != JD_OK) return first_err;
   ++pipelined_sections_;
   // the exchange slot was written before the section's last barrier and read after it
-  const int pos = prod.out_kind - BUF_SLOT_A, pis = prod.in_kind - BUF_SLOT_A;
+  const int pos = slot_of(prod.out_kind), pis = slot_of(prod.in_kind);
   if (pis >= 0) slot_read_[pis] = host_epoch_;
   if (pos >= 0) {
     slot_written_[pos] = host_epoch_ - 1;
@@ -296,7 +303,7 @@ int Runtime::run_pipelined(Plan& pl, int plan_id, size_t index, const void* in, 
   return JD_OK;
 }
 
-int Runtime::execute(int plan_id, const void* in, void* out, void* stream) {
+int Runtime::execute(int plan_id, const void* in, void* out, void* stream, void* const* peer_out) {
   Plan& pl = plans_.at(plan_id);
   if (world_ > 1 || pl.slot_bytes > 0) {
     if (!arena_ || (size_t)pl.slot_bytes > slot_bytes_) {
@@ -304,6 +311,19 @@ int Runtime::execute(int plan_id, const void* in, void* out, void* stream) {
       return JD_ERR_INVALID_ARG;
     }
   }
+  bool wants_peer_out = false;
+  for (const PlanStep& st : pl.steps) wants_peer_out |= st.out_kind == BUF_PEER_OUT;
+  if (wants_peer_out && (peer_out == nullptr || peer_out[me_] != out)) {
+    set_last_error("runtime: plan stores into the peers' result blocks but their addresses were not given");
+    return JD_ERR_INVALID_ARG;
+  }
+  // cleared on every way out, so that a later call can never see this call's addresses
+  struct PeerOutScope {
+    void* const*& slot;
+    ~PeerOutScope() { slot = nullptr; }
+  } peer_scope{cur_peer_out_};
+  cur_peer_out_ = peer_out;
+  bool peer_stores_pending = false;
   StepProfiler& prof = StepProfiler::instance();
   for (size_t i = 0; i < pl.steps.size(); ++i) {
     PlanStep& st = pl.steps[i];
@@ -315,6 +335,11 @@ int Runtime::execute(int plan_id, const void* in, void* out, void* stream) {
     }
     int rc = sync_before(st, stream);
     if (rc != JD_OK) return rc;
+    if (st.out_kind == BUF_PEER_OUT && world_ > 1 && !st.copy_only && st.desc.npeers > 1) {
+      // the other ranks may still be using their result blocks in work issued before this call
+      if ((rc = barrier(stream)) != JD_OK) return rc;
+      peer_stores_pending = true;
+    }
     const bool profiling = prof.mode() != StepProfiler::OFF;
     if (profiling) {
       char name[96];
@@ -328,10 +353,12 @@ int Runtime::execute(int plan_id, const void* in, void* out, void* stream) {
     rc = launch_step(pl, plan_id, i, nullptr, in, out, stream);
     if (profiling) prof.stop(stream);
     if (rc != JD_OK) return rc;
-    const int is = st.in_kind - BUF_SLOT_A, os = st.out_kind - BUF_SLOT_A;
+    const int is = slot_of(st.in_kind), os = slot_of(st.out_kind);
     if (is >= 0) slot_read_[is] = host_epoch_;
     if (os >= 0) slot_written_[os] = host_epoch_;
   }
+  // the result is complete once every rank's stores into it have landed
+  if (peer_stores_pending) return barrier(stream);
   return JD_OK;
 }
 

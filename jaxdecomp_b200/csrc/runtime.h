@@ -34,7 +34,14 @@ enum BufferKind : int32_t {
   BUF_USER_OUT = 1,  // the result tensor passed to execute()
   BUF_SLOT_A = 2,    // arena slot 0 (peer visible)
   BUF_SLOT_B = 3,    // arena slot 1 (peer visible)
+  // The result tensor when it lives in a peer-visible block that every rank allocated alike: peer p's
+  // copy is peer_out[p] of execute().  An exchange pass stores straight into the other ranks' results,
+  // so no copy out of a slot follows it; execute() puts one barrier before the pass (nobody may still
+  // be using its result block from an earlier call) and one at the end (every store has landed).
+  BUF_PEER_OUT = 4,
 };
+// Index of the arena slot a buffer kind names, or -1.
+inline int slot_of(int kind) { return (kind == BUF_SLOT_A || kind == BUF_SLOT_B) ? kind - BUF_SLOT_A : -1; }
 
 struct PlanStep {
   PassDesc desc;               // pointers of in/out are filled in at execution time
@@ -86,7 +93,9 @@ class Runtime {
   void clear_plans();
 
   // execution
-  int execute(int plan_id, const void* in, void* out, void* stream);
+  // peer_out: base address of the result block on every arena rank (world entries), needed by plans
+  // that have a BUF_PEER_OUT step; peer_out[me] must equal out.
+  int execute(int plan_id, const void* in, void* out, void* stream, void* const* peer_out = nullptr);
   // 0 disables the pipelined execution of plans (every step then runs in order on the caller's stream)
   void set_pipelining(bool on) { pipelining_ = on; }
   bool pipelining() const { return pipelining_; }
@@ -124,6 +133,7 @@ class Runtime {
   long long timeout_ns_ = 10000000000LL;
   // hazard tracking (identical on every rank because all ranks issue the same sequence)
   long long host_epoch_ = 0;
+  void* const* cur_peer_out_ = nullptr;    // peer_out of the execute() call in progress
   long long slot_written_[2] = {-1, -1};  // epoch during which peers last wrote the slot
   long long slot_read_[2] = {-1, -1};     // epoch during which this rank last read the slot
   std::map<std::string, int> plan_index_;

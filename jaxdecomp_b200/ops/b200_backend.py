@@ -17,7 +17,7 @@ from __future__ import annotations
 
 import atexit
 import os
-from typing import Dict, List, Sequence, Tuple
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 import torch.distributed as dist
@@ -38,6 +38,14 @@ _TUNING_ENV = ("JD_B200_TILE_T", "JD_B200_BULK", "JD_B200_INTRAPAD", "JD_B200_RO
                "JD_B200_PIPE_MIN_BYTES")
 # exchange passes smaller than this (bytes per rank) are not pipelined: below it the extra launches and
 # per-chunk barriers cost more than the overlap gains
+def auto_pipeline_ctas(npeers: int) -> int:
+    """Thread-block limit of a pipelined exchange chunk when the configuration leaves it open
+    (``pipeline_ctas = -1``).  With two peers half of the pass's traffic stays local and 96 of the 148 SMs
+    were the best setting measured; with four and eight peers the exchange is the longer of the two
+    overlapped passes and 112 blocks were faster (1024^3 complex64 round trips on 2, 4 and 8 B200s)."""
+    return 96 if npeers <= 2 else 112
+
+
 _PIPE_MIN_BYTES = 256 << 20
 
 
@@ -130,7 +138,10 @@ class MeshRuntime:
         return self.ranks.index(self.mesh.rank_of(coords))
 
     def build_plan(self, key: str, steps: Sequence[Step], lshape, dtype, inverse: bool, scale: float, nbatch: int,
-                   fused_mul=None):
+                   fused_mul=None, peer_out: bool = False):
+        """Compile ``steps`` into a native plan.  ``peer_out``: the result tensor is a peer-visible block
+        that every rank allocated alike; when the last pass is an exchange it then stores straight into
+        the other ranks' result blocks instead of into a workspace slot that is copied out afterwards."""
         nat = self.nat
         eb = torch.empty((), dtype=dtype).element_size()
         coords = self.mesh.coords[-2:]
@@ -165,6 +176,8 @@ class MeshRuntime:
             last = i == n - 1
             if not remote and (last or i + 1 >= tail_plain_from):
                 out_kind = nat.BUF_USER_OUT
+            elif remote and last and peer_out:
+                out_kind = nat.BUF_PEER_OUT
             else:
                 out_kind = next_slot
                 next_slot = nat.BUF_SLOT_B if next_slot == nat.BUF_SLOT_A else nat.BUF_SLOT_A
@@ -185,8 +198,9 @@ class MeshRuntime:
                 if cut is None or plan_steps[i].out_kind == nat.BUF_USER_OUT:
                     continue
                 plan_steps[i].pipe_role, plan_steps[i + 1].pipe_role, plan_steps[i].pipe_chunks = cut
-                plan_steps[i].pipe_grid_limit = int(config.pipeline_ctas)
-        if cur_kind != nat.BUF_USER_OUT:
+                limit = int(config.pipeline_ctas)
+                plan_steps[i].pipe_grid_limit = limit if limit >= 0 else auto_pipeline_ctas(specs[i].npeers)
+        if cur_kind not in (nat.BUF_USER_OUT, nat.BUF_PEER_OUT):
             st = nat.PlanStep()
             st.in_kind = cur_kind
             st.out_kind = nat.BUF_USER_OUT
@@ -209,8 +223,12 @@ class MeshRuntime:
         return c >= 8 and (c & (c - 1)) == 0
 
     def run_steps(self, x: torch.Tensor, steps: Sequence[Step], inverse: bool, scale: float,
-                  fused_mul=None) -> torch.Tensor:
-        """Execute a step list on a local block.  ``fused_mul = (n_orig, offsets, box)`` makes the result a
+                  fused_mul=None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Execute a step list on a local block.  ``out``: a contiguous tensor of the result's shape and
+        dtype to write into (collective: every rank passes one or none).  When it is a peer-visible block
+        (``ops/peer.py``) and the last pass is an exchange, the exchange stores straight into the other
+        ranks' ``out`` blocks and the copy out of the workspace disappears.
+  ``fused_mul = (n_orig, offsets, box)`` makes the result a
         batch of three: entry b is the pipeline applied to ``x * i k_b / k^2`` (``x`` in the rotated layout of
         ``pfft3d``, ``offsets`` the global indices of its first element), with the multiplier applied inside
         the first pass instead of by a kernel of its own."""
@@ -229,15 +247,23 @@ class MeshRuntime:
         env = tuple(os.environ.get(k, "") for k in _TUNING_ENV)
         fkey = None if fused_mul is None else (tuple(fused_mul[0]), tuple(int(o) for o in fused_mul[1]),
                                                tuple(float(b) for b in fused_mul[2]))
-        pykey = (tuple(steps), lshape, x.dtype, bool(inverse), float(scale), nbatch, env, config.snapshot(), fkey)
+        peer_hit = None
+        if out is not None and self.world > 1 and os.environ.get("JD_B200_PEER_OUT", "1") != "0":
+            from . import peer as _peer
+
+            peer_hit = _peer.lookup(self.mesh, out)
+        pykey = (tuple(steps), lshape, x.dtype, bool(inverse), float(scale), nbatch, env, config.snapshot(), fkey,
+                 peer_hit is not None)
         hit = self._pycache.get(pykey)
         if hit is None:
             if not _passes._group_steps(steps, self.mesh.pdims):
-                return x.clone()  # every step is an exchange over a single rank: the identity
+                # every step is an exchange over a single rank: the identity
+                return x.clone() if out is None else out.copy_(x.reshape(out.shape))
             key = "|".join(map(str, pykey + (self.mesh.pdims, self.mesh.coords[-2:])))
             pid = self.rt.find_plan(key)
             if pid < 0:
-                pid, final_shape = self.build_plan(key, steps, lshape, x.dtype, inverse, scale, nbatch, fused_mul)
+                pid, final_shape = self.build_plan(key, steps, lshape, x.dtype, inverse, scale, nbatch, fused_mul,
+                                                   peer_out=peer_hit is not None)
                 self._shapes[pid] = final_shape
             hit = self._pycache[pykey] = (pid, self._shapes[pid], self.rt.plan_slot_bytes(pid))
         else:
@@ -245,9 +271,20 @@ class MeshRuntime:
         pid, final_shape, need = hit
         if need > 0 or self.world > 1:
             self.ensure_arena(max(need, 1))
-        out = torch.empty(((nbatch,) if nb else ()) + tuple(final_shape), dtype=x.dtype, device=x.device)
+        oshape = ((nbatch,) if nb else ()) + tuple(final_shape)
+        if out is None:
+            out = torch.empty(oshape, dtype=x.dtype, device=x.device)
+        elif (tuple(out.shape) != oshape or out.dtype != x.dtype or not out.is_contiguous() or out.data_ptr() % 16
+              or out.device != x.device):
+            raise ValueError(f"out must be a contiguous, 16-byte aligned {x.dtype} tensor of shape {oshape} on {x.device}")
+        elif out.data_ptr() == x.data_ptr():
+            raise ValueError("out must not be the operand")
         self.check_status()
-        self.rt.execute(pid, x.data_ptr(), out.data_ptr(), _stream())
+        if peer_hit is not None:
+            alloc, offset = peer_hit
+            self.rt.execute_peer_out(pid, x.data_ptr(), [p + offset for p in alloc.ptrs], _stream())
+        else:
+            self.rt.execute(pid, x.data_ptr(), out.data_ptr(), _stream())
         return out
 
     # ---- halos -------------------------------------------------------------------------------------
@@ -367,8 +404,8 @@ def get_runtime(mesh: Mesh) -> MeshRuntime:
 
 
 def run_steps(x: torch.Tensor, steps: Sequence[Step], mesh: Mesh, inverse: bool, scale: float,
-              fused_mul=None) -> torch.Tensor:
-    return get_runtime(mesh).run_steps(x, steps, inverse, scale, fused_mul)
+              fused_mul=None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    return get_runtime(mesh).run_steps(x, steps, inverse, scale, fused_mul, out)
 
 
 def halo_exchange(x, extents, periods, mesh: Mesh, inplace: bool = False) -> torch.Tensor:

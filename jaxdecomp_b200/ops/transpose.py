@@ -17,15 +17,16 @@ from . import plan as _plan
 from .dispatch import resolve_backend
 
 
-def _run(x, mesh, kind, contiguous, backend):
+def _run(x, mesh, kind, contiguous, backend, out=None):
     steps = _plan.transpose_steps(kind, contiguous)
     if backend == "b200":
         from . import b200_backend
 
-        return b200_backend.run_steps(x, steps, mesh, False, 1.0)
+        return b200_backend.run_steps(x, steps, mesh, False, 1.0, out=out)
     from . import torch_backend
 
-    return torch_backend.run_steps(x, steps, mesh, False)
+    y = torch_backend.run_steps(x, steps, mesh, False)
+    return y if out is None else out.copy_(y)
 
 
 class _Transpose(torch.autograd.Function):
@@ -54,7 +55,15 @@ class _Transpose(torch.autograd.Function):
         return _vmap_leading(_Transpose.apply, in_dims, x, args)
 
 
-def transpose(x, kind: str, backend: str = "auto"):
+def transpose(x, kind: str, backend: str = "auto", out=None):
+    """One of the six transposes, ``kind`` in ``x_y, y_z, z_y, y_x, x_z, z_x``.
+
+    ``out`` (a tensor or :class:`ShardedTensor` of the result's local shape and dtype; every rank passes
+    one or none) receives the result, as ``out=`` does in ``torch``: no gradient flows through such a
+    call.  On the native backend a peer-visible ``out`` (``jd.empty_peer_visible`` / ``jd.empty_sharded``,
+    the same view on every rank) lets the exchange store straight into the other ranks' result blocks:
+    one barrier before and one after the pass replace the staging slot and the copy out of it.
+    """
     st, plain = as_sharded(x)
     mesh = st.mesh
     contiguous = bool(config.transpose_axis_contiguous)
@@ -66,7 +75,13 @@ def transpose(x, kind: str, backend: str = "auto"):
         _plan.check_input_spec(steps, spec, mesh.pdims, names)
     _, out_spec = _plan.propagate(steps, tuple(st.local.shape[nb:]), spec, mesh.pdims, names)
     b = resolve_backend(backend, st.local)
-    y = _Transpose.apply(st.local.contiguous(), mesh, kind, contiguous, b)
+    if out is not None:
+        dest = out.local if isinstance(out, ShardedTensor) else out
+        if torch.is_grad_enabled() and (st.local.requires_grad or dest.requires_grad):
+            raise RuntimeError("transpose(..., out=...) does not support automatic differentiation")
+        y = _run(st.local.contiguous(), mesh, kind, contiguous, b, out=dest)
+    else:
+        y = _Transpose.apply(st.local.contiguous(), mesh, kind, contiguous, b)
     if plain:
         return y
     return ShardedTensor(y, mesh, tuple(st.spec[:nb]) + tuple(out_spec))
@@ -81,31 +96,31 @@ def transpose_shard(x: torch.Tensor, kind: str, mesh, backend: str = "auto") -> 
     return _Transpose.apply(x.contiguous(), mesh, kind, contiguous, b)
 
 
-def transposeXtoY(x, backend: str = "auto"):
+def transposeXtoY(x, backend: str = "auto", out=None):
     """X-pencil -> Y-pencil: global ``(N0,N1,N2)`` -> ``(N2,N0,N1)`` (contiguous mode)."""
-    return transpose(x, "x_y", backend)
+    return transpose(x, "x_y", backend, out)
 
 
-def transposeYtoZ(x, backend: str = "auto"):
+def transposeYtoZ(x, backend: str = "auto", out=None):
     """Y-pencil -> Z-pencil."""
-    return transpose(x, "y_z", backend)
+    return transpose(x, "y_z", backend, out)
 
 
-def transposeZtoY(x, backend: str = "auto"):
+def transposeZtoY(x, backend: str = "auto", out=None):
     """Z-pencil -> Y-pencil."""
-    return transpose(x, "z_y", backend)
+    return transpose(x, "z_y", backend, out)
 
 
-def transposeYtoX(x, backend: str = "auto"):
+def transposeYtoX(x, backend: str = "auto", out=None):
     """Y-pencil -> X-pencil."""
-    return transpose(x, "y_x", backend)
+    return transpose(x, "y_x", backend, out)
 
 
-def transposeXtoZ(x, backend: str = "auto"):
+def transposeXtoZ(x, backend: str = "auto", out=None):
     """X-pencil -> Z-pencil in one exchange over the first mesh axis."""
-    return transpose(x, "x_z", backend)
+    return transpose(x, "x_z", backend, out)
 
 
-def transposeZtoX(x, backend: str = "auto"):
+def transposeZtoX(x, backend: str = "auto", out=None):
     """Z-pencil -> X-pencil in one exchange over the first mesh axis."""
-    return transpose(x, "z_x", backend)
+    return transpose(x, "z_x", backend, out)

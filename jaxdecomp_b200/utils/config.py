@@ -115,8 +115,9 @@ class DecompConfig:
     by a local pass is cut into ``pipeline_chunks`` chunks, and the local pass
     works on chunk k while chunk k+1 crosses NVLink.  ``pipeline_ctas`` limits
     the thread blocks of an exchange chunk (0: no limit) so that the local pass
-    finds free SMs; the default, 96 of the 148 SMs, was the best or within 1 %
-    of the best setting on 2 and 4 GPUs.
+    finds free SMs; the default, -1, picks the limit from the number of peers
+    of the exchange (96 of the 148 SMs for two peers, 112 for more: the best
+    settings measured on 2, 4 and 8 GPUs).
     """
 
     halo_comm_backend: HaloCommBackend = HALO_COMM_P2P
@@ -126,7 +127,7 @@ class DecompConfig:
     wait_timeout_ms: int = int(os.environ.get("JD_B200_WAIT_TIMEOUT_MS", "10000"))
     reference_compat_halo_grad: bool = False
     pipeline_chunks: int = int(os.environ.get("JD_B200_PIPE_CHUNKS", "4"))
-    pipeline_ctas: int = int(os.environ.get("JD_B200_PIPE_CTAS", "96"))
+    pipeline_ctas: int = int(os.environ.get("JD_B200_PIPE_CTAS", "-1"))
 
     def update(self, key, value):
         names = {f.name for f in fields(self)}
@@ -140,8 +141,8 @@ class DecompConfig:
             value = HaloCommBackend(int(value))
         elif key in ("pipeline_chunks", "pipeline_ctas", "wait_timeout_ms"):
             value = int(value)
-            if value < 0:
-                raise ValueError(f"{key} must not be negative")
+            if value < (-1 if key == "pipeline_ctas" else 0):
+                raise ValueError(f"{key} must not be negative" + (" (-1: automatic)" if key == "pipeline_ctas" else ""))
         setattr(self, key, value)
 
     @property

@@ -86,6 +86,16 @@ def _transpose_worker(rank, world, pdims, contiguous):
             assert torch.equal(zz.gather(), xg.permute(1, 2, 0) if contiguous else xg)
             xx = jd.transposeZtoX(zz)
             assert torch.equal(xx.gather(), xg)
+        # out=: the result lands in the given tensor (plain or sharded), without autograd
+        dest = jd.empty_sharded(mesh, tuple(y.local.shape), dtype, spec=y.spec, peer_visible=False)
+        got = jd.transposeXtoY(x, out=dest)
+        assert got.local.data_ptr() == dest.local.data_ptr() and torch.equal(dest.local, y.local)
+        raw = torch.empty_like(z.local)
+        jd.transposeYtoZ(y, out=raw)
+        assert torch.equal(raw, z.local)
+    xr = jd.ShardedTensor(x.local.real.clone().requires_grad_(True), mesh)
+    with pytest.raises(RuntimeError, match="automatic differentiation"):
+        jd.transposeXtoY(xr, out=torch.empty_like(jd.transposeXtoY(xr).local))
 
 
 @pytest.mark.parametrize("pdims,contiguous", [((2, 4), True), ((4, 2), False), ((1, 8), True), ((8, 1), True)])

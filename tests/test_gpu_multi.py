@@ -55,6 +55,35 @@ def _transposes_case(x, mesh, pencil):
         assert torch.equal(jd.transposeZtoX(zz, backend="b200").local, x.local)
 
 
+def _peer_out_transposes(x, mesh, pencil):
+    """``out=`` on a peer-visible block: the exchange stores straight into the other ranks' results (a
+    barrier, the pass, a barrier: no staging slot, no copy out of it); an ordinary ``out`` is filled too."""
+    from jaxdecomp_b200.ops import b200_backend
+
+    rt = b200_backend.get_runtime(mesh)
+    kinds = ["XtoY", "YtoZ", "ZtoY", "YtoX"] + (["XtoZ", "ZtoX"] if pencil else [])
+    cur = {"X": x}
+    for kind in kinds:
+        src_p, dst_p = kind[0], kind[-1]
+        fn = getattr(jd, "transpose" + kind)
+        src = cur[src_p]
+        want = fn(src, backend="torch")
+        pv = jd.empty_sharded(mesh, tuple(want.local.shape), want.local.dtype, spec=want.spec)
+        pv.local.fill_(-1)
+        before = rt.rt.launches()
+        got = fn(src, backend="b200", out=pv)
+        n = rt.rt.launches() - before
+        assert got.local.data_ptr() == pv.local.data_ptr() and tuple(got.spec) == tuple(want.spec), kind
+        assert torch.equal(pv.local, want.local), kind
+        exchanged = mesh.pdims[0 if kind in ("YtoZ", "ZtoY", "XtoZ", "ZtoX") else 1] > 1
+        assert n <= (3 if exchanged else 1), (kind, n)
+        plain_out = torch.full_like(want.local, -1)
+        fn(src, backend="b200", out=plain_out)
+        assert torch.equal(plain_out, want.local), kind
+        cur[dst_p] = want
+        jd.free_peer_visible(mesh)
+
+
 def _ops_worker(rank, world):
     from jaxdecomp_b200.ops import b200_backend
 
@@ -83,11 +112,14 @@ def _ops_worker(rank, world):
                 _fft_case(x, mesh, tol, (pdims, contiguous, dtype, shape))
                 if contiguous and shape[2] == 1024:
                     _transposes_case(x, mesh, p0 > 1 and p1 > 1)
+                    _peer_out_transposes(x, mesh, p0 > 1 and p1 > 1)
                 del x
             # transposes, exact
             for dtype in (torch.float32, torch.complex128):
                 xg = torch.randn((16, 32, 64), generator=torch.Generator().manual_seed(7), dtype=torch.float64).to(dtype)
                 _transposes_case(jd.shard(xg.to(dev), mesh), mesh, p0 > 1 and p1 > 1)
+                if dtype == torch.float32:
+                    _peer_out_transposes(jd.shard(xg.to(dev), mesh), mesh, p0 > 1 and p1 > 1)
         jd.config.update("transpose_axis_contiguous", True)
         assert rt.rt.pipelined_sections() > 0
         assert rt.arena_generation == grew, "the reserved workspace should have covered every case"

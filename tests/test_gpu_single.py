@@ -99,6 +99,17 @@ def test_transposes_single_gpu(dtype):
     assert torch.equal(z, x.permute(1, 2, 0))
     assert torch.equal(jd.transposeYtoX(jd.transposeZtoY(z, backend="b200"), backend="b200"), x)
     assert torch.equal(jd.transposeZtoX(jd.transposeXtoZ(x, backend="b200"), backend="b200"), x)
+    # out=: the rotation is written into the given tensor, also one that lives in a peer-visible block
+    dest = torch.full_like(y, 7)
+    assert jd.transposeXtoY(x, backend="b200", out=dest).data_ptr() == dest.data_ptr()
+    assert torch.equal(dest, y)
+    with jd.single_rank_mesh() as mesh:
+        pv = jd.empty_peer_visible(mesh, tuple(z.shape), dtype)
+        jd.transposeYtoZ(y, backend="b200", out=pv)
+        assert torch.equal(pv, z)
+        jd.free_peer_visible(mesh)
+    with pytest.raises(ValueError):
+        jd.transposeXtoY(x, backend="b200", out=torch.empty((3, 3, 3), device=_dev(), dtype=dtype))
 
 
 def test_fft_gradient_matches_torch():

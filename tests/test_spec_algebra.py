@@ -130,6 +130,24 @@ def test_config_update_validates_keys():
         jd.pfft3d(torch.zeros(2, 2, 2), backend="bogus")
 
 
+def test_pipeline_block_limit_setting():
+    from jaxdecomp_b200.ops.b200_backend import auto_pipeline_ctas
+
+    old = jd.config.pipeline_ctas
+    try:
+        jd.config.update("pipeline_ctas", -1)        # automatic: chosen per exchange from its number of peers
+        jd.config.update("pipeline_ctas", 0)         # no limit
+        jd.config.update("pipeline_ctas", "64")
+        assert jd.config.pipeline_ctas == 64
+        with pytest.raises(ValueError):
+            jd.config.update("pipeline_ctas", -2)
+        with pytest.raises(ValueError):
+            jd.config.update("pipeline_chunks", -1)
+    finally:
+        jd.config.update("pipeline_ctas", old)
+    assert 0 < auto_pipeline_ctas(2) <= auto_pipeline_ctas(8) <= 148
+
+
 def test_pass_compiler_geometry():
     steps = plan.fft_steps(jd.PENCILS, False, True, native=True)
     specs, final = passes.compile_passes(steps, (4, 4, 32), (2, 4), (1, 2))
