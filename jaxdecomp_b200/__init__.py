@@ -45,6 +45,7 @@ from .utils.api import (
     GridConfig,
     autotune,
     finalize,
+    check_peers,
     get_autotuned_config,
     get_fft_workspace_size,
     get_halo_workspace_size,
@@ -92,7 +93,7 @@ __version__ = "0.1.0"
 
 __all__ = [
     "config", "init", "finalize", "get_pencil_info", "get_autotuned_config", "make_config", "autotune",
-    "get_fft_workspace_size", "get_transpose_workspace_size", "get_halo_workspace_size", "reserve_workspace",
+    "get_fft_workspace_size", "get_transpose_workspace_size", "get_halo_workspace_size", "reserve_workspace", "check_peers",
     "halo_exchange", "halo_exchange_", "halo_accumulate", "halo_reduce", "pad_halo", "unpad_halo",
     "pfft3d", "pifft3d", "fftfreq3d", "rfftfreq3d",
     "transposeXtoY", "transposeYtoX", "transposeYtoZ", "transposeZtoY", "transposeXtoZ", "transposeZtoX",

@@ -44,11 +44,19 @@ def make_config(gdims=(0, 0, 0), pdims=(1, 1), transpose_comm_backend=TRANSPOSE_
 
 
 _initialised = False
+_monitor = None  # parallel.protocol.HealthMonitor started by init(heartbeat=...)
 
 
-def init(workspace_bytes: Optional[int] = None) -> None:
+def init(workspace_bytes: Optional[int] = None, heartbeat: Optional[float] = None, heartbeat_max_age: Optional[float] = None) -> None:
     """Load the native core eagerly on machines with a GPU.  Optional: every op
     initialises what it needs on first use.
+
+    ``heartbeat`` (seconds) starts a host-side liveness monitor: every rank publishes a time stamp
+    through the process group's store at that period, and :func:`check_peers` raises
+    :class:`~jaxdecomp_b200.parallel.protocol.PeerDeadError` for ranks whose last stamp is older than
+    ``heartbeat_max_age`` (default: ten periods).  Call :func:`check_peers` between steps, before
+    launching kernels that would wait on a peer that is gone; the device-side waits stay bounded
+    either way.
 
     ``workspace_bytes`` pre-sizes the peer-visible workspace: every arena created afterwards holds
     at least that many bytes per exchange buffer (there are two), so that no later, larger problem
@@ -63,7 +71,21 @@ def init(workspace_bytes: Optional[int] = None) -> None:
         from ..ops import b200_backend
 
         b200_backend.set_default_workspace(int(workspace_bytes))
+    global _monitor
+    if heartbeat is not None and _monitor is None and dist.is_available() and dist.is_initialized() \
+            and dist.get_world_size() > 1:
+        from ..parallel.protocol import HealthMonitor
+
+        period = float(heartbeat)
+        _monitor = HealthMonitor(period=period, max_age=float(heartbeat_max_age or 10 * period))
     _initialised = True
+
+
+def check_peers() -> None:
+    """Raise :class:`~jaxdecomp_b200.parallel.protocol.PeerDeadError` when a rank has stopped publishing its
+    heartbeat (see :func:`init`); a no-op without a monitor.  Host-side only: nothing is launched."""
+    if _monitor is not None:
+        _monitor.check()
 
 
 def reserve_workspace(mesh, slot_bytes: int) -> None:
@@ -79,7 +101,10 @@ def finalize() -> None:
     more than one rank is in use; safe to call repeatedly.  A later op simply
     re-creates what it needs (this is also the recovery path after a reported
     peer time-out)."""
-    global _initialised
+    global _initialised, _monitor
+    if _monitor is not None:
+        _monitor.stop()
+        _monitor = None
     try:
         from ..ops import b200_backend
 

@@ -72,6 +72,31 @@ def test_heartbeat_detects_quiet_rank():
     run_ranks(_heartbeat_worker, 4)
 
 
+def _public_heartbeat_worker(rank, world):
+    import jaxdecomp_b200 as jd
+
+    jd.check_peers()  # no monitor yet: nothing to check
+    jd.init(heartbeat=0.05, heartbeat_max_age=0.6)
+    dist.barrier()
+    time.sleep(0.3)
+    jd.check_peers()
+    dist.barrier()
+    if rank == 1:
+        jd.finalize()  # stops publishing; the rank leaves between steps
+        time.sleep(2.0)
+        return
+    time.sleep(1.2)
+    with pytest.raises(PeerDeadError) as ei:
+        jd.check_peers()
+    assert ei.value.ranks == [1]
+    jd.finalize()
+    jd.check_peers()  # the monitor is gone again
+
+
+def test_heartbeat_through_init_and_check_peers():
+    run_ranks(_public_heartbeat_worker, 3)
+
+
 def _missing_rank_worker(rank, world):
     t = torch.ones(4)
     dist.all_reduce(t)
