@@ -95,6 +95,8 @@ PYBIND11_MODULE(_jdb200, m) {
       RW(Cl) RW(Tl) RW(Ol) RW(npeers) RW(fft_mode) RW(M) RW(inverse) RW(T) RW(Cc) RW(pitch) RW(elem_bytes)
       RW(load_t_contig) RW(store_t_contig) RW(use_bulk) RW(mul_mode) RW(vec_in) RW(vec_out) RW(intra_pad) RW(logT) RW(logW) RW(split_axis) RW(scale) RW(grid_limit) RW(out_limit)
 #undef RW
+      // the descriptor as the kernels see it (a plain struct); read by the sanitizer self-test program
+      .def("raw_bytes", [](const PassDesc& d) { return py::bytes(reinterpret_cast<const char*>(&d), sizeof(PassDesc)); })
       .def_property("in_ptr", [](const PassDesc& d) { return (uintptr_t)d.in; },
                     [](PassDesc& d, uintptr_t v) { d.in = P(v); })
       .def_property("twiddle", [](const PassDesc& d) { return (uintptr_t)d.twiddle; },

@@ -148,6 +148,72 @@ def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False, 
             fcntl.flock(lock, fcntl.LOCK_UN)
 
 
+HOST_SELFTEST_SOURCES = ["host_selftest.cpp", "cpu_ref.cpp", "tables.cpp"]
+
+
+_SAN_FLAGS = ["-fsanitize=address,undefined", "-fno-sanitize-recover=all"]
+_sanitizer_cxx: Optional[str] = None
+
+
+def sanitizer_compiler() -> Optional[str]:
+    """A C++ compiler that can link a program with the AddressSanitizer and UndefinedBehaviorSanitizer
+    run-times (``$CXX`` first, then ``g++`` on the path), or ``None``."""
+    global _sanitizer_cxx
+    if _sanitizer_cxx is not None:
+        return _sanitizer_cxx or None
+    import tempfile
+
+    cands = [c for c in (os.environ.get("CXX"), shutil.which("g++"), "/usr/bin/g++") if c]
+    with tempfile.TemporaryDirectory() as tmp:
+        src = Path(tmp) / "probe.cpp"
+        src.write_text("int main() { return 0; }\n")
+        for cxx in dict.fromkeys(cands):
+            try:
+                r = subprocess.run([cxx, *_SAN_FLAGS, str(src), "-o", str(Path(tmp) / "probe")], capture_output=True)
+            except OSError:
+                continue
+            if r.returncode == 0:
+                _sanitizer_cxx = cxx
+                return cxx
+    _sanitizer_cxx = ""
+    return None
+
+
+def build_host_selftest(force: bool = False) -> Path:
+    """Compile the host side of the core (CPU emulation of the tile pass, table construction) together
+    with ``csrc/host_selftest.cpp`` into a stand-alone program under AddressSanitizer and
+    UndefinedBehaviorSanitizer (``g++ -fsanitize=address,undefined``, reports abort the program).  The
+    program replays pass descriptors written by the planner; ``tests/test_sanitizer_cpu.py`` drives it.
+    Needs g++ with the sanitizer run-times and the CUDA headers and run-time library (``tables.cpp`` also
+    holds the device-table path, which this program never takes); no GPU."""
+    cxx = sanitizer_compiler()
+    nvcc = _nvcc()
+    if cxx is None or nvcc is None:
+        raise NativeExtensionError("no C++ compiler with the sanitizer run-times, or no CUDA toolkit: cannot build "
+                                   "the sanitizer self-test")
+    cuda_root = Path(nvcc).resolve().parent.parent
+    out_dir = _CSRC / "build_sanitize"
+    out_dir.mkdir(parents=True, exist_ok=True)
+    exe, stamp = out_dir / "host_selftest", out_dir / "host_selftest.hash"
+    with open(out_dir / ".lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if exe.exists() and stamp.exists() and stamp.read_text().strip() == _source_hash() and not force:
+                return exe
+            libdir = next((d for d in (cuda_root / "lib64", cuda_root / "targets" / "x86_64-linux" / "lib")
+                           if (d / "libcudart.so").exists()), cuda_root / "lib64")
+            cmd = [cxx, "-std=c++17", "-O1", "-g", "-fno-omit-frame-pointer", *_SAN_FLAGS, "-I", str(cuda_root / "include"), "-I", str(_CSRC),
+                   *[str(_CSRC / s) for s in HOST_SELFTEST_SOURCES], "-o", str(exe),
+                   "-L", str(libdir), f"-Wl,-rpath,{libdir}", "-lcudart", "-lpthread", "-ldl"]
+            r = subprocess.run(cmd, capture_output=True, text=True)
+            if r.returncode != 0:
+                raise NativeExtensionError(f"sanitizer self-test failed to build:\n{r.stdout}\n{r.stderr}")
+            stamp.write_text(_source_hash())
+            return exe
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+
+
 def load(build_if_needed: bool = True):
     """Import the native module, building it first if it is missing or stale."""
     global _module, _load_error
