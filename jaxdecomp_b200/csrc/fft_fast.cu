@@ -242,13 +242,12 @@ __device__ __forceinline__ void fast_stage(cx<R>* sm, cx<R>* rowp, int j, int sg
 
 // One tile: rows [t0, t0 + T) of (o, b).
 template <typename Cfg, typename R, bool MUL = false>
-__device__ __forceinline__ void fast_tile(const PassDesc& d, cx<R>* sm, int tile, int tiles_t, int tid) {
+__device__ __forceinline__ void fast_tile(const PassDesc& d, cx<R>* sm, int tile, int tiles_t, int tid, int b) {
   using E = cx<R>;
   constexpr int UPR = Cfg::UPR;
   constexpr bool STORE_T = Cfg::STORE_T;
   const int tt = tile % tiles_t;
   const int o = tile / tiles_t;
-  const int b = blockIdx.y;
   const int t0 = tt << Cfg::LOGT;
   const bool inv = d.inverse != 0;
 
@@ -323,7 +322,7 @@ __device__ __forceinline__ void fast_tile(const PassDesc& d, cx<R>* sm, int tile
 // the loop, the compiler kept addresses of the next iteration live and spilled up to 190 bytes).
 template <typename Cfg, typename R>
 __device__ __noinline__ void fast_tile_call(const PassDesc& d, cx<R>* sm, int tile, int tiles_t) {
-  fast_tile<Cfg, R>(d, sm, tile, tiles_t, threadIdx.x);
+  fast_tile<Cfg, R>(d, sm, tile, tiles_t, threadIdx.x, blockIdx.y);
 }
 
 // VARIANT 0: one tile per block.  VARIANT 1: the grid is smaller than the number of tiles
@@ -340,9 +339,12 @@ __global__ void __launch_bounds__((FastCfg<R, LOGM, LOGT, STORE_T>::NT), (FastCf
   if (pass_aborted(d)) return;
   const int tiles_t = d.Tn >> LOGT;
   if constexpr (VARIANT == 2) {
-    fast_tile<Cfg, R, true>(d, sm, blockIdx.x, tiles_t, threadIdx.x);
+    // The batch entries of a fused pass read the same operand (is_b = 0) and differ only in the multiplier:
+    // with the batch as the fastest block index the blocks of one tile run at the same time and the
+    // operand comes from DRAM once, from L2 for the others.
+    fast_tile<Cfg, R, true>(d, sm, blockIdx.x / d.B, tiles_t, threadIdx.x, blockIdx.x % d.B);
   } else if constexpr (!LOOP) {
-    fast_tile<Cfg, R>(d, sm, blockIdx.x, tiles_t, threadIdx.x);
+    fast_tile<Cfg, R>(d, sm, blockIdx.x, tiles_t, threadIdx.x, blockIdx.y);
   } else {
     const int ntiles = tiles_t * d.On;
     for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
@@ -401,7 +403,7 @@ template <typename R, int LOGM, int LOGT, bool STORE_T>
 static int launch_fast_t(const PassDesc& d, cudaStream_t stream) {
   using Cfg = FastCfg<R, LOGM, LOGT, STORE_T>;
   const long long nblocks = (long long)(d.Tn >> LOGT) * d.On;
-  if (nblocks > 2147483647LL || d.B > 65535) {
+  if (nblocks * (d.mul_mode != JD_MUL_NONE ? d.B : 1) > 2147483647LL || d.B > 65535) {
     set_last_error("fast pass: grid too large");
     return JD_ERR_INVALID_ARG;
   }
@@ -422,7 +424,8 @@ static int launch_fast_t(const PassDesc& d, cudaStream_t stream) {
     configured[variant] = true;
   }
   const long long grid = loop ? d.grid_limit : nblocks;
-  kern<<<dim3((unsigned)grid, (unsigned)d.B, 1), Cfg::NT, Cfg::SMEM, stream>>>(d);
+  const dim3 blocks = mul ? dim3((unsigned)(nblocks * d.B), 1, 1) : dim3((unsigned)grid, (unsigned)d.B, 1);
+  kern<<<blocks, Cfg::NT, Cfg::SMEM, stream>>>(d);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_last_error(cudaGetErrorString(e));

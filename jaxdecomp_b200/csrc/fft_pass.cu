@@ -266,6 +266,10 @@ int launch_pass(const PassDesc& d, void* stream_, StatusBlock* status) {
   }
   if (d.fft_mode == JD_FFT_MIXED) return launch_mixed_pass(d, stream_);
   if (d.fft_mode == JD_COPY) {
+    if (copy_fast_eligible(d)) {
+      const char* off = std::getenv("JD_B200_COPY_FAST");
+      if (!(off && off[0] == '0')) return launch_copy_fast(d, stream_);
+    }
     if (d.elem_bytes == 4) return launch_t<float, false, 1>(d, stream, status);
     if (d.elem_bytes == 8) return launch_t<cx<float>, false, 1>(d, stream, status);
     return launch_t<cx<double>, false, 1>(d, stream, status);

@@ -11,6 +11,11 @@ namespace jdb {
 // ---- tile pass (fft_pass.cu / cpu_ref.cpp) ---------------------------------------------------------
 int validate_pass(const PassDesc& d);
 int run_pass_host(const PassDesc& d);
+// Rotating copy passes of 8- and 16-byte elements whose extents are multiples of the tile (copy_fast.cu):
+// launch_pass uses them instead of the general kernel's copy mode.  Eligibility looks at the addresses too
+// (16-byte alignment), so it is decided at launch time.  JD_B200_COPY_FAST=0 switches them off.
+bool copy_fast_eligible(const PassDesc& d);
+int launch_copy_fast(const PassDesc& d, void* stream);
 // Launch on `stream`.  Returns a Status; CUDA launch errors are reported as JD_ERR_CUDA
 // and the message is available from last_error_message().
 int launch_pass(const PassDesc& d, void* stream, StatusBlock* status);

@@ -54,6 +54,7 @@ SOURCES = [
     "trace.cpp",
     "cpu_ref.cpp",
     "fft_pass.cu",
+    "copy_fast.cu",
     "fft_fast.cu", "fft_mixed.cu", "fft_mixed_sa.cu", "fft_mixed_sb.cu", "fft_mixed_sc.cu",
     "signal.cu",
     "halo.cu",

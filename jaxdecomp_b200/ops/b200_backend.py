@@ -35,9 +35,9 @@ _runtimes: Dict[tuple, "MeshRuntime"] = {}
 _default_slot_bytes = 0
 # switches that change how a plan is tiled: part of the plan key
 _TUNING_ENV = ("JD_B200_TILE_T", "JD_B200_BULK", "JD_B200_INTRAPAD", "JD_B200_ROWPAD", "JD_B200_FAST",
-               "JD_B200_PIPE_MIN_BYTES")
-# exchange passes smaller than this (bytes per rank) are not pipelined: below it the extra launches and
-# per-chunk barriers cost more than the overlap gains
+               "JD_B200_PIPE_MIN_BYTES", "JD_B200_COPY_T", "JD_B200_COPY_CC", "JD_B200_COPY_PAD", "JD_B200_COPY_FAST")
+
+
 def auto_pipeline_ctas(npeers: int) -> int:
     """Thread-block limit of a pipelined exchange chunk when the configuration leaves it open
     (``pipeline_ctas = -1``).  With two peers half of the pass's traffic stays local and 96 of the 148 SMs
@@ -46,6 +46,8 @@ def auto_pipeline_ctas(npeers: int) -> int:
     return 96 if npeers <= 2 else 112
 
 
+# exchange passes smaller than this (bytes per rank) are not pipelined: below it the extra launches and
+# per-chunk barriers cost more than the overlap gains
 _PIPE_MIN_BYTES = 256 << 20
 
 

@@ -313,10 +313,12 @@ def choose_tiling(spec: PassSpec, elem_bytes: int, remote: bool) -> dict:
     else:
         out["fft_mode"] = 0
         out["M"] = 0
-        Cc = 64 if elem_bytes <= 8 else 32
-        Cc = min(Cc, _next_pow2(C))
-        T = min(32, _next_pow2(Tn))
+        Cc = _env_int("JD_B200_COPY_CC") or (64 if elem_bytes <= 8 else 32)
+        Cc = min(_next_pow2(Cc), _next_pow2(C))
+        T = min(_next_pow2(_env_int("JD_B200_COPY_T") or 32), _next_pow2(Tn))
         pad = {4: 1, 8: 2, 16: 1}[elem_bytes] if (load_t or store_t) and T > 1 else 0
+        if _env_int("JD_B200_COPY_PAD") is not None and pad:
+            pad = _env_int("JD_B200_COPY_PAD")
         out["T"] = T
         out["Cc"] = Cc
         out["pitch"] = Cc + pad

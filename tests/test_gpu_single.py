@@ -90,9 +90,10 @@ def test_fft_non_contiguous_mode_and_batch():
         jd.config.update("transpose_axis_contiguous", True)
 
 
+@pytest.mark.parametrize("shape", [(12, 20, 36), (64, 128, 192)])   # general copy kernel / 64x64-tile kernel
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float64, torch.complex64, torch.complex128])
-def test_transposes_single_gpu(dtype):
-    x = torch.randn((12, 20, 36), device=_dev(), dtype=dtype)
+def test_transposes_single_gpu(dtype, shape):
+    x = torch.randn(shape, device=_dev(), dtype=dtype)
     y = jd.transposeXtoY(x, backend="b200")
     assert torch.equal(y, x.permute(2, 0, 1))
     z = jd.transposeYtoZ(y, backend="b200")
@@ -110,6 +111,20 @@ def test_transposes_single_gpu(dtype):
         jd.free_peer_visible(mesh)
     with pytest.raises(ValueError):
         jd.transposeXtoY(x, backend="b200", out=torch.empty((3, 3, 3), device=_dev(), dtype=dtype))
+    # a batch, and the tile kernels against the general one
+    xb = torch.stack([x, 2 * x])
+    assert torch.equal(jd.transposeXtoY(xb, backend="b200"), xb.permute(0, 3, 1, 2))
+
+
+def test_rotating_copy_kernels_match_the_general_kernel(monkeypatch):
+    for dtype in (torch.complex64, torch.complex128, torch.float64):
+        x = torch.randn((128, 64, 256), device=_dev(), dtype=dtype)
+        fast = [jd.transposeXtoY(x, backend="b200"), jd.transposeYtoX(x, backend="b200")]
+        monkeypatch.setenv("JD_B200_COPY_FAST", "0")
+        slow = [jd.transposeXtoY(x, backend="b200"), jd.transposeYtoX(x, backend="b200")]
+        monkeypatch.delenv("JD_B200_COPY_FAST")
+        assert torch.equal(fast[0], slow[0]) and torch.equal(fast[1], slow[1])
+        assert torch.equal(fast[0], x.permute(2, 0, 1)) and torch.equal(fast[1], x.permute(1, 2, 0))
 
 
 def test_fft_gradient_matches_torch():
