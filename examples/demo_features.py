@@ -77,6 +77,10 @@ def tour(rank, world, tmpdir):
     say("Y pencil equals the global permute(2, 0, 1):", torch.equal(y.gather(), g.permute(2, 0, 1)))
     say("Z -> Y -> X restores x exactly:", torch.equal(jd.transposeYtoX(jd.transposeZtoY(z)).local, x.local))
     say("X -> Z in one exchange:", jd.transposeXtoZ(x))
+    dest = jd.empty_sharded(mesh, tuple(y.local.shape), y.local.dtype, spec=y.spec)   # peer-visible on GPUs
+    jd.transposeXtoY(x, out=dest)
+    say("out= writes into a preallocated block (on GPUs the exchange stores straight into it):",
+        torch.equal(dest.local, y.local))
 
     # ------------------------------------------------------------------------------------------
     section("5. halo exchange")
