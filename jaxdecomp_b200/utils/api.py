@@ -209,28 +209,43 @@ def get_autotuned_config(grid_config: GridConfig, double_precision: bool = False
                          disable_nvshmem_backends: bool = True, tune_with_transpose: bool = True,
                          halo_extents: Sequence[int] = (0, 0, 0),
                          halo_periods: Sequence[bool] = (True, True, True)) -> GridConfig:
-    """Return a copy of ``grid_config`` with ``pdims`` (and both transports)
+    """Return a copy of ``grid_config`` with ``pdims`` and both transports
     chosen by measurement: the transposes of an FFT round trip when
     ``tune_with_transpose`` else a halo exchange with the given extents.  The
-    signature follows the reference's seven positional arguments; the two
-    ``disable_*`` flags select between the peer-store kernels and the NCCL
-    baseline as candidates."""
+    signature follows the reference's seven positional arguments.  Candidates
+    on a GPU: the peer-store kernels with the pipelined transport, the same
+    without pipelining, and (unless ``disable_nccl_backends``) the NCCL
+    baseline; every candidate is timed on every admissible process grid and the
+    fastest pair wins.  On a CPU only the library collectives exist."""
     dtype = torch.complex128 if double_precision else torch.complex64
     halo = None
     if not tune_with_transpose:
         halo = ((int(halo_extents[0]), int(halo_extents[1])), (bool(halo_periods[0]), bool(halo_periods[1])))
-    backends = ["auto"] if disable_nccl_backends else ["auto", "torch"]
-    best = None
-    for b in backends:
-        pd, timings = autotune(grid_config.gdims, dtype=dtype, backend=b, halo=halo, return_timings=True)
-        if best is None or timings[pd] < best[2]:
-            best = (pd, b, timings[pd])
-    native = best[1] == "auto" and torch.cuda.is_available()
-    from .config import HALO_COMM_NCCL, TRANSPOSE_COMM_NCCL
+    from .config import HALO_COMM_NCCL, TRANSPOSE_COMM_NCCL, TRANSPOSE_COMM_P2P_PL
 
-    return GridConfig(tuple(grid_config.gdims), tuple(best[0]),
-                      TRANSPOSE_COMM_P2P if native else TRANSPOSE_COMM_NCCL,
-                      HALO_COMM_P2P if native else HALO_COMM_NCCL)
+    # candidates: (op backend, transpose transport); the peer-store kernels with and without pipelining
+    # (only the transposes of an FFT have a pipelined form), then the library collectives
+    native_ok = torch.cuda.is_available()
+    cands = []
+    if native_ok:
+        cands.append(("auto", TRANSPOSE_COMM_P2P_PL if tune_with_transpose else TRANSPOSE_COMM_P2P))
+        if tune_with_transpose:
+            cands.append(("auto", TRANSPOSE_COMM_P2P))
+    if not disable_nccl_backends or not cands:
+        cands.append(("torch" if native_ok else "auto", TRANSPOSE_COMM_NCCL))
+    saved = config.transpose_comm_backend
+    best = None
+    try:
+        for b, transport in cands:
+            if b == "auto" and native_ok:
+                config.update("transpose_comm_backend", transport)
+            pd, timings = autotune(grid_config.gdims, dtype=dtype, backend=b, halo=halo, return_timings=True)
+            if best is None or timings[pd] < best[2]:
+                best = (pd, transport, timings[pd])
+    finally:
+        config.update("transpose_comm_backend", saved)
+    native = best[1] != TRANSPOSE_COMM_NCCL
+    return GridConfig(tuple(grid_config.gdims), tuple(best[0]), best[1], HALO_COMM_P2P if native else HALO_COMM_NCCL)
 
 
 def _workspace_bytes(gdims, pdims, elem_bytes: int, slots: int) -> int:

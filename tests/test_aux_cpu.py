@@ -115,6 +115,36 @@ def test_autotune_picks_a_valid_process_grid():
     run_ranks(_autotune_worker, 4)
 
 
+def test_autotuned_config_chooses_among_transports(monkeypatch):
+    """Candidate logic of get_autotuned_config with stand-in timings: pipelined peer stores, plain peer
+    stores, library collectives; the configuration is left as it was found."""
+    from jaxdecomp_b200.utils import api
+
+    cost = {}
+
+    def fake_autotune(shape, dtype=None, backend="auto", halo=None, return_timings=False, **kw):
+        key = "nccl" if backend == "torch" else jd.TransposeCommBackend(int(jd.config.transpose_comm_backend)).name
+        timings = {(1, 4): cost[key], (2, 2): cost[key] + 1.0}
+        return ((1, 4), timings) if return_timings else (1, 4)
+
+    monkeypatch.setattr(api, "autotune", fake_autotune)
+    monkeypatch.setattr(api.torch.cuda, "is_available", lambda: True)
+    before = jd.config.transpose_comm_backend
+    grid = jd.make_config((16, 16, 16), (1, 4))
+    cost.update({"TRANSPOSE_COMM_P2P_PL": 1.0, "TRANSPOSE_COMM_P2P": 2.0, "nccl": 3.0})
+    cfg = jd.get_autotuned_config(grid)
+    assert cfg.transpose_comm_backend == jd.TRANSPOSE_COMM_P2P_PL and cfg.halo_comm_backend == jd.HALO_COMM_P2P
+    cost.update({"TRANSPOSE_COMM_P2P_PL": 2.5, "TRANSPOSE_COMM_P2P": 2.0})
+    assert jd.get_autotuned_config(grid).transpose_comm_backend == jd.TRANSPOSE_COMM_P2P
+    cost.update({"nccl": 0.5})
+    cfg = jd.get_autotuned_config(grid)
+    assert cfg.transpose_comm_backend == jd.TRANSPOSE_COMM_NCCL and cfg.halo_comm_backend == jd.HALO_COMM_NCCL
+    assert jd.get_autotuned_config(grid, False, True).transpose_comm_backend == jd.TRANSPOSE_COMM_P2P   # NCCL excluded
+    # tuning on a halo exchange has no pipelined candidate
+    assert jd.get_autotuned_config(grid, False, True, True, False, (2, 2, 0)).transpose_comm_backend == jd.TRANSPOSE_COMM_P2P
+    assert jd.config.transpose_comm_backend == before
+
+
 def test_init_finalize_are_idempotent():
     jd.init()
     jd.finalize()
