@@ -17,7 +17,7 @@ from __future__ import annotations
 
 import atexit
 import os
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import Dict, List, Optional, Sequence
 
 import torch
 import torch.distributed as dist

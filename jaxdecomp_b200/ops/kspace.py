@@ -12,7 +12,7 @@ All operators are linear and differentiable.
 from __future__ import annotations
 
 import math
-from typing import Optional, Sequence, Tuple
+from typing import Sequence, Tuple
 
 import torch
 

@@ -27,7 +27,7 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import List, Sequence, Tuple, Union
 
-from ..utils.config import NO_DECOMP, PENCILS, SLAB_XY, SLAB_YZ, Decomposition
+from ..utils.config import SLAB_XY, Decomposition
 
 
 @dataclass(frozen=True)

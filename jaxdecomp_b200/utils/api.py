@@ -9,8 +9,7 @@ Parity targets in the reference's native module: ``init``/``finalize``
 """
 from __future__ import annotations
 
-import itertools
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import List, Optional, Sequence, Tuple
 
 import torch

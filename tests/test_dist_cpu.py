@@ -1,6 +1,5 @@
 """Distributed ops on eight CPU ranks (gloo), baseline backend, checked against
 single-process torch: forward FFT, round trip, transposes, halos, gradients."""
-import itertools
 
 import pytest
 import torch

@@ -1,7 +1,6 @@
 """Failure detection without touching a GPU: the signalling protocol model
 with withheld and corrupted signals, heartbeats with a rank that goes quiet,
 and a collective that one rank never joins."""
-import os
 import time
 
 import pytest
