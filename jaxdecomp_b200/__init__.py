@@ -17,7 +17,8 @@ aliases so that code written against the reference runs unchanged.
 """
 from __future__ import annotations
 
-from .ops.fft import fftfreq3d, pfft3d, pifft3d, rfftfreq3d
+from . import fft, halo, transpose  # noqa: F401  (module paths of the reference: jaxdecomp.fft.pfft3d, ...)
+from .ops.fft import fftfreq3d, pfft3d, pifft3d, pirfft3d, prfft3d, rfftfreq3d
 from .ops.halo import halo_accumulate, halo_exchange, halo_exchange_, halo_reduce, pad_halo, unpad_halo
 from .ops.peer import empty_peer_visible, empty_sharded, free_peer_visible
 from .ops.transpose import (
@@ -95,7 +96,7 @@ __all__ = [
     "config", "init", "finalize", "get_pencil_info", "get_autotuned_config", "make_config", "autotune",
     "get_fft_workspace_size", "get_transpose_workspace_size", "get_halo_workspace_size", "reserve_workspace", "check_peers",
     "halo_exchange", "halo_exchange_", "halo_accumulate", "halo_reduce", "pad_halo", "unpad_halo",
-    "pfft3d", "pifft3d", "fftfreq3d", "rfftfreq3d",
+    "pfft3d", "pifft3d", "prfft3d", "pirfft3d", "fftfreq3d", "rfftfreq3d", "fft", "halo", "transpose",
     "transposeXtoY", "transposeYtoX", "transposeYtoZ", "transposeZtoY", "transposeXtoZ", "transposeZtoX",
     "transpose_shard",
     "TRANSPOSE_XY", "TRANSPOSE_YX", "TRANSPOSE_YZ", "TRANSPOSE_ZY", "TRANSPOSE_XZ", "TRANSPOSE_ZX",

@@ -163,6 +163,19 @@ def test_pass_compiler_geometry():
     assert t["fft_mode"] == 2 and t["M"] == 64 and t["vec_in"] == 0
 
 
+def test_module_paths_of_the_reference():
+    """``jaxdecomp.fft.pfft3d``, ``jaxdecomp.halo.halo_exchange`` and ``jaxdecomp.transpose.transposeXtoY`` have
+    the same paths here; the real-input transforms exist and refuse, as in the reference
+    (``src/jaxdecomp/fft.py:127-128, 214-284``)."""
+    x = torch.randn(4, 6, 8)
+    assert torch.equal(jd.fft.pfft3d(x), jd.pfft3d(x)) and jd.fft.pifft3d is jd.pifft3d
+    assert jd.halo.halo_exchange is jd.halo_exchange and jd.transpose.transposeXtoY is jd.transposeXtoY
+    assert jd.fft.fftfreq3d is jd.fftfreq3d and jd.fft.rfftfreq3d is jd.rfftfreq3d
+    for fn in (jd.fft.prfft3d, jd.fft.pirfft3d, jd.prfft3d):
+        with pytest.raises(NotImplementedError):
+            fn(x)
+
+
 def test_single_rank_plain_tensor_api():
     x = torch.randn(8, 4, 16)
     k = jd.pfft3d(x)
