@@ -4,7 +4,7 @@
 // transports: GPU 0 stores 512 MiB into GPU 1's memory (then, for comparison, into its own) in runs of
 // 128 or 256 bytes that lie 512 KiB apart -- the pattern of a rotated store of the tile passes -- with
 // 8-byte or 16-byte stores per lane, for grids of 8...296 blocks of 256 or 1024 threads.  Plain peer
-// stores only: no TMA, no multicast, no waits between kernels.  CUDA events around two launches after
+// stores only: no bulk copies, no waits between kernels.  CUDA events around two launches after
 // one warm-up launch.
 //
 //   nvcc -O3 -gencode arch=compute_100a,code=sm_100a -o peer_store_bandwidth benchmarks/peer_store_bandwidth.cu
