@@ -167,3 +167,19 @@ def _compat_grad_worker(rank, world):
 
 def test_reference_compatible_halo_gradient_rule():
     run_ranks(_compat_grad_worker, 4)
+
+
+def test_gradcheck_and_double_backward_on_a_single_rank():
+    """Numerical first and second derivatives of every differentiable op (float64, one rank)."""
+    x = torch.randn((3, 4, 5), dtype=torch.float64, generator=torch.Generator().manual_seed(80), requires_grad=True)
+    z = torch.randn((3, 4, 5), dtype=torch.complex128, generator=torch.Generator().manual_seed(81), requires_grad=True)
+    for norm in ("backward", "ortho"):
+        assert torch.autograd.gradcheck(lambda v: torch.view_as_real(jd.pfft3d(v, norm=norm)), (x,))
+        assert torch.autograd.gradcheck(lambda v: jd.pifft3d(jd.pfft3d(v, norm=norm), norm=norm), (z,))
+    assert torch.autograd.gradgradcheck(lambda v: torch.view_as_real(jd.pfft3d(v)).pow(2), (x,))
+    for fn in (jd.transposeXtoY, jd.transposeYtoZ, jd.transposeZtoY, jd.transposeYtoX, jd.transposeXtoZ, jd.transposeZtoX):
+        assert torch.autograd.gradcheck(fn, (x,))
+        assert torch.autograd.gradgradcheck(lambda v: fn(v).pow(3), (x,))
+    with jd.single_rank_mesh():
+        assert torch.autograd.gradcheck(lambda v: jd.halo_exchange(v, (1, 1), (True, True)), (x,))
+        assert torch.autograd.gradcheck(lambda v: jd.halo_accumulate(v, (1, 1), (True, True)), (x,))
