@@ -147,6 +147,10 @@ PYBIND11_MODULE(_jdb200, m) {
   m.def("fast_pass_eligible", [](const PassDesc& d) { return fast_pass_eligible(d); });
   m.def("pass_threads", &pass_threads);
   m.def("pass_smem_bytes", &pass_smem_bytes);
+  m.def("copy_fast_eligible", [](const PassDesc& d) { return copy_fast_eligible(d); },
+        "True when launch_pass would run the rotating copy kernels of copy_fast.cu on this (filled) descriptor");
+  m.def("run_copy_fast_host", [](const PassDesc& d) { raise_on(run_copy_fast_host(d), "run_copy_fast_host"); },
+        "Host restatement of the rotating copy kernels (same thread mapping and addressing), for CPU tests");
   m.def("get_fft_tables", [](int C, int M, int elem_bytes, bool device) {
     FftTables t = get_fft_tables(C, M, elem_bytes, device);
     return py::make_tuple((uintptr_t)t.twiddle, (uintptr_t)t.chirp, (uintptr_t)t.bhat, (uintptr_t)t.tw_stage);

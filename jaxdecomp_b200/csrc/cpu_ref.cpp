@@ -4,6 +4,7 @@
 // It lets the planner, the peer addressing and the FFT numerics be tested on a
 // machine without a GPU, with the buffers of all emulated ranks living in one
 // process.  It is a test vehicle, not a product path.
+#include <cstdint>
 #include <cstring>
 #include <vector>
 
@@ -140,6 +141,126 @@ int run_pass_host(const PassDesc& d) {
     std::snprintf(msg, sizeof(msg), "store outside the destination buffer: peer %d, element offset %lld, buffer of %lld elements",
                   m.peer, m.off, m.limit);
     set_last_error(msg);
+    return JD_ERR_BOUNDS;
+  }
+  return JD_OK;
+}
+
+// ---- host twin of the rotating copy kernels ---------------------------------------------------------------
+// copy_rotate8_kernel / copy_rotate16_kernel (copy_fast.cu) restated for the host: the same decomposition
+// into blocks, warps and lanes, the same swizzled (or odd-pitch) shared-memory tile, the same destination
+// arithmetic, executed serially -- so that their addressing on every mesh shape, including the peers of a
+// column or of a tile's rows, is tested against the general pass without a GPU.  A restatement, not shared
+// code: it has to be kept in step with the kernels by hand.
+namespace {
+
+struct Unit16 {
+  uint64_t lo, hi;
+};
+
+struct HostTile {
+  int c0, t0, o, b;
+};
+
+HostTile host_tile_of_block(const PassDesc& d, long long bid, int b, int TC, int TT) {
+  const int tiles_c = d.C / TC, tiles_t = d.Tn / TT;
+  HostTile tc;
+  tc.c0 = (int)(bid % tiles_c) * TC;
+  bid /= tiles_c;
+  tc.t0 = (int)(bid % tiles_t) * TT;
+  tc.o = (int)(bid / tiles_t);
+  tc.b = b;
+  return tc;
+}
+
+// count elements of EB bytes each at element offset off of peer's buffer
+template <typename T>
+void host_checked_store(const PassDesc& d, int peer, long long off, const T* src, int count) {
+  if (!store_in_bounds(d, peer, off, count)) return;
+  std::memcpy((T*)d.out[peer] + off, src, sizeof(T) * (size_t)count);
+}
+
+void copy_rotate8_host(const PassDesc& d) {
+  constexpr int TC = 64, TT = 64, UNITS = TT / 2, WARPS = 8;
+  const long long nblocks = (long long)(d.C / TC) * (d.Tn / TT) * d.On;
+  std::vector<Unit16> sm((size_t)TC * UNITS);
+  for (int b = 0; b < d.B; ++b)
+    for (long long bid = 0; bid < nblocks; ++bid) {
+      const HostTile tc = host_tile_of_block(d, bid, b, TC, TT);
+      for (int warp = 0; warp < WARPS; ++warp)
+        for (int lane = 0; lane < 32; ++lane) {
+          const uint64_t* in = (const uint64_t*)d.in + ((long long)tc.o * d.is_o + (long long)tc.b * d.is_b +
+                                                        (long long)tc.t0 * d.is_t + tc.c0 + 2 * lane);
+          const int sw_w = lane & 7;
+          for (int it = 0; it < 4; ++it) {
+            const int tp = it * 8 + warp;
+            const uint64_t* p = in + (long long)(2 * tp) * d.is_t;
+            const uint64_t r00 = p[0], r01 = p[1], r10 = p[d.is_t], r11 = p[d.is_t + 1];
+            sm[(size_t)(2 * lane) * UNITS + (tp ^ sw_w)] = Unit16{r00, r10};
+            sm[(size_t)(2 * lane + 1) * UNITS + (tp ^ sw_w)] = Unit16{r01, r11};
+          }
+        }
+      const OutBase ob = out_base_for(d, tc.o, tc.b);
+      const int pt = d.split_axis == 2 ? tc.t0 / d.Tl : 0;
+      for (int warp = 0; warp < WARPS; ++warp)
+        for (int lane = 0; lane < 32; ++lane) {
+          const long long toff = ob.off + (long long)(tc.t0 - pt * d.Tl + 2 * lane);
+          for (int it = 0; it < 8; ++it) {
+            const int c = it * 8 + warp;
+            const Unit16 v = sm[(size_t)c * UNITS + (lane ^ ((c >> 1) & 7))];
+            const int gc = tc.c0 + c;
+            const int pc = d.split_axis == 1 ? gc / d.Cl : 0;
+            const uint64_t pair[2] = {v.lo, v.hi};
+            host_checked_store<uint64_t>(d, ob.peer + pc + pt, toff + (long long)(gc - pc * d.Cl) * d.os_c, pair, 2);
+          }
+        }
+    }
+}
+
+void copy_rotate16_host(const PassDesc& d) {
+  constexpr int TC = 32, TT = 32, PITCH = TC + 1, WARPS = 8;
+  const long long nblocks = (long long)(d.C / TC) * (d.Tn / TT) * d.On;
+  std::vector<Unit16> sm((size_t)TT * PITCH);
+  for (int b = 0; b < d.B; ++b)
+    for (long long bid = 0; bid < nblocks; ++bid) {
+      const HostTile tc = host_tile_of_block(d, bid, b, TC, TT);
+      for (int warp = 0; warp < WARPS; ++warp)
+        for (int lane = 0; lane < 32; ++lane) {
+          const Unit16* in = (const Unit16*)d.in + ((long long)tc.o * d.is_o + (long long)tc.b * d.is_b +
+                                                    (long long)tc.t0 * d.is_t + tc.c0 + lane);
+          for (int it = 0; it < 4; ++it) sm[(size_t)(it * 8 + warp) * PITCH + lane] = in[(long long)(it * 8 + warp) * d.is_t];
+        }
+      const OutBase ob = out_base_for(d, tc.o, tc.b);
+      const int pt = d.split_axis == 2 ? tc.t0 / d.Tl : 0;
+      for (int warp = 0; warp < WARPS; ++warp)
+        for (int lane = 0; lane < 32; ++lane) {
+          const long long toff = ob.off + (long long)(tc.t0 - pt * d.Tl + lane);
+          for (int it = 0; it < 4; ++it) {
+            const int c = it * 8 + warp;
+            const Unit16 v = sm[(size_t)lane * PITCH + c];
+            const int gc = tc.c0 + c;
+            const int pc = d.split_axis == 1 ? gc / d.Cl : 0;
+            host_checked_store<Unit16>(d, ob.peer + pc + pt, toff + (long long)(gc - pc * d.Cl) * d.os_c, &v, 1);
+          }
+        }
+    }
+}
+
+}  // namespace
+
+// Runs the host twin on a descriptor that copy_fast_eligible() accepted (the caller checks).
+int run_copy_fast_host(const PassDesc& d) {
+  int rc = validate_pass(d);
+  if (rc != JD_OK) return rc;
+  if (d.fft_mode != JD_COPY || (d.elem_bytes != 8 && d.elem_bytes != 16)) return JD_ERR_INVALID_ARG;
+  if (pass_aborted(d)) return JD_OK;
+  host_bounds_miss() = BoundsMiss{0, 0, 0, 0};
+  if (d.elem_bytes == 8)
+    copy_rotate8_host(d);
+  else
+    copy_rotate16_host(d);
+  if (host_bounds_miss().hit) {
+    set_last_error("rotating copy pass: store outside the destination buffer");
     return JD_ERR_BOUNDS;
   }
   return JD_OK;

@@ -16,6 +16,8 @@ int run_pass_host(const PassDesc& d);
 // (16-byte alignment), so it is decided at launch time.  JD_B200_COPY_FAST=0 switches them off.
 bool copy_fast_eligible(const PassDesc& d);
 int launch_copy_fast(const PassDesc& d, void* stream);
+// Host restatement of those kernels (cpu_ref.cpp), for tests of their addressing without a GPU.
+int run_copy_fast_host(const PassDesc& d);
 // Launch on `stream`.  Returns a Status; CUDA launch errors are reported as JD_ERR_CUDA
 // and the message is available from last_error_message().
 int launch_pass(const PassDesc& d, void* stream, StatusBlock* status);

@@ -11,7 +11,7 @@ unit tests; not a product path.
 """
 from __future__ import annotations
 
-from typing import List, Sequence
+from typing import List, Optional, Sequence
 
 import torch
 
@@ -41,7 +41,8 @@ def split_blocks(x: torch.Tensor, pdims: Sequence[int], spec_axes=(0, 1)) -> Lis
 
 
 def emulate_steps(blocks: List[torch.Tensor], steps: Sequence[Step], pdims: Sequence[int], inverse: bool = False,
-                  scale: float = 1.0, pipeline_chunks: int = 0, fused_mul=None) -> List[torch.Tensor]:
+                  scale: float = 1.0, pipeline_chunks: int = 0, fused_mul=None, copy_twin: bool = False,
+                  stats: Optional[dict] = None) -> List[torch.Tensor]:
     """Run a step list on the blocks of all ranks (row-major rank order) and
     return the per-rank results.
 
@@ -53,7 +54,11 @@ def emulate_steps(blocks: List[torch.Tensor], steps: Sequence[Step], pdims: Sequ
     chunk would see zeros and the result would differ.
 
     ``fused_mul = (n_orig, offsets_per_rank, box)`` runs the first pass with the fused k-space multiplier
-    (three batch entries read from the one input block, entry b multiplied by ``i k_b / k^2``)."""
+    (three batch entries read from the one input block, entry b multiplied by ``i k_b / k^2``).
+
+    ``copy_twin`` runs every copy pass that the GPU would hand to the rotating copy kernels
+    (``csrc/copy_fast.cu``) through their host restatement instead of the general pass; ``stats``, when
+    given, receives ``{"twin_passes": n}``."""
     from .. import native as _native
 
     nat = _native.require()
@@ -105,6 +110,7 @@ def emulate_steps(blocks: List[torch.Tensor], steps: Sequence[Step], pdims: Sequ
         return d
 
     i = 0
+    twin_passes = 0
     while i < npass:
         cut = None
         if pipeline_chunks >= 2 and i + 1 < npass:
@@ -112,7 +118,12 @@ def emulate_steps(blocks: List[torch.Tensor], steps: Sequence[Step], pdims: Sequ
         if cut is None:
             nxt = alloc(i)
             for r in range(world):
-                nat.run_pass_host(desc(i, r, cur, nxt))
+                d = desc(i, r, cur, nxt)
+                if copy_twin and nat.copy_fast_eligible(d):
+                    nat.run_copy_fast_host(d)
+                    twin_passes += 1
+                else:
+                    nat.run_pass_host(d)
             cur = nxt
             i += 1
             continue
@@ -129,4 +140,6 @@ def emulate_steps(blocks: List[torch.Tensor], steps: Sequence[Step], pdims: Sequ
                 nat.run_pass_host(cd[r].restricted(crole, k * step, step))
         cur = nxt
         i += 2
+    if stats is not None:
+        stats["twin_passes"] = twin_passes
     return cur

@@ -5,7 +5,7 @@ import pytest
 import torch
 
 from jaxdecomp_b200 import native
-from jaxdecomp_b200.ops import emulate, plan
+from jaxdecomp_b200.ops import emulate, passes, plan
 from jaxdecomp_b200.parallel.mesh import pencil_type_from_pdims
 
 pytestmark = pytest.mark.skipif(not native.available(), reason="native core could not be built (no nvcc)")
@@ -87,6 +87,52 @@ def test_transposes(contig, dtype):
         want = x.permute(perm) if contig else x
         full = _assemble(cur, pdims, spec, names, tuple(want.shape))
         assert torch.equal(full, want), kind
+
+
+@pytest.mark.parametrize("pdims", [(1, 1), (1, 4), (4, 1), (2, 2), (2, 4), (4, 2)])
+@pytest.mark.parametrize("dtype", [torch.complex64, torch.complex128, torch.float64])
+def test_rotating_copy_kernels_addressing_on_every_mesh(pdims, dtype):
+    """The rotating copy kernels (64 x 64 / 32 x 32 tiles, ``csrc/copy_fast.cu``) in their host restatement:
+    the chain of all six transposes on slabs, pencils and a single rank, against the global permutation."""
+    names = ("a0", "a1")
+    n = 64 * max(pdims)          # every local extent of every pencil orientation is a multiple of the 64-wide tile
+    shape = (n, n, n)
+    x = torch.randn(shape, dtype=dtype, generator=torch.Generator().manual_seed(12))
+    cur = emulate.split_blocks(x, pdims)
+    spec = _xspec(pdims, names)
+    used = 0
+    kinds = [("x_y", (2, 0, 1)), ("y_z", (1, 2, 0)), ("z_y", (2, 0, 1)), ("y_x", (0, 1, 2))]
+    if pdims[0] > 1 and pdims[1] > 1:
+        kinds += [("x_z", (1, 2, 0)), ("z_x", (0, 1, 2))]
+    for kind, perm in kinds:
+        steps = plan.transpose_steps(kind, True)
+        lshape = cur[0].shape
+        stats = {}
+        cur = emulate.emulate_steps(cur, steps, pdims, copy_twin=True, stats=stats)
+        used += stats["twin_passes"]
+        _, spec = plan.propagate(steps, lshape, spec, pdims, names)
+        full = _assemble(cur, pdims, spec, names, tuple(x.permute(perm).shape))
+        assert torch.equal(full, x.permute(perm)), kind
+    # every pass of every rank went through the tile kernels' restatement
+    assert used == len(kinds) * pdims[0] * pdims[1]
+
+
+def test_rotating_copy_kernels_are_not_chosen_for_other_shapes():
+    nat = native.require()
+    for lshape, eb, want in (((64, 64, 128), 8, True), ((64, 64, 128), 4, False), ((60, 64, 128), 8, True), ((64, 60, 128), 8, False),
+                             ((32, 32, 32), 16, True), ((32, 32, 32), 8, False)):
+        specs, _ = passes.compile_passes(plan.transpose_steps("x_y", True), lshape, (1, 1), (0, 0))
+        d = passes.fill_desc(nat, specs[0], eb, False, 1.0, 1, remote=False, device_tables=False)
+        buf = torch.zeros(specs[0].numel * eb + 64, dtype=torch.uint8)
+        d.in_ptr = buf.data_ptr()
+        d.set_out(0, buf.data_ptr())
+        assert nat.copy_fast_eligible(d) == want, (lshape, eb)
+        d.in_ptr = buf.data_ptr() + 8            # an operand that is not 16-byte aligned
+        assert nat.copy_fast_eligible(d) == (want and eb == 16), (lshape, eb)
+    # the non-contiguous layout mode moves no axes: not a rotating pass
+    specs, _ = passes.compile_passes(plan.transpose_steps("x_y", False), (64, 64, 128), (1, 2), (0, 0))
+    d = passes.fill_desc(nat, specs[0], 8, False, 1.0, 1, remote=True, device_tables=False)
+    assert not nat.copy_fast_eligible(d)
 
 
 def test_batched_blocks():
