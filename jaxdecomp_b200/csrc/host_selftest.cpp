@@ -9,8 +9,9 @@
 // a bad shift in the index arithmetic is an UndefinedBehaviorSanitizer report (both abort the program).
 // The results go to a second file, where the test compares them bit for bit with the regular build.
 //
-// Case file: u64 magic, u64 sizeof(PassDesc), u64 number of cases; per case the raw PassDesc, u64
-// operand bytes, the operand, u64 number of destinations, u64 bytes of each destination.
+// Case file: u64 magic, u64 sizeof(PassDesc), u64 number of cases; per case the raw PassDesc, u64 mode
+// (0: the general tile pass, 1: the host restatement of the rotating copy kernels), u64 operand bytes,
+// the operand, u64 number of destinations, u64 bytes of each destination.
 // Result file: per case, per destination, the destination's bytes.
 #include <cstdint>
 #include <cstdio>
@@ -31,7 +32,7 @@ const char* last_error_message() { return g_selftest_error.c_str(); }
 
 namespace {
 
-constexpr uint64_t kMagic = 0x31464C455342444AULL;  // "JDBSELF1"
+constexpr uint64_t kMagic = 0x32464C455342444AULL;  // "JDBSELF2"
 
 bool read_exact(std::FILE* f, void* dst, size_t n) { return n == 0 || std::fread(dst, 1, n, f) == n; }
 
@@ -53,8 +54,10 @@ int main(int argc, char** argv) {
   if (head[1] != sizeof(jdb::PassDesc)) return fail("descriptor size differs from the library's");
   for (uint64_t c = 0; c < head[2]; ++c) {
     jdb::PassDesc d;
-    uint64_t in_bytes = 0, nout = 0;
-    if (!read_exact(in, &d, sizeof(d)) || !read_exact(in, &in_bytes, 8)) return fail("truncated case");
+    uint64_t mode = 0, in_bytes = 0, nout = 0;
+    if (!read_exact(in, &d, sizeof(d)) || !read_exact(in, &mode, 8) || !read_exact(in, &in_bytes, 8))
+      return fail("truncated case");
+    if (mode > 1) return fail("unknown mode");
     // exact-size heap blocks: the red zones around them are what catches a stray index
     unsigned char* operand = static_cast<unsigned char*>(std::malloc(in_bytes ? in_bytes : 1));
     if (!operand || !read_exact(in, operand, in_bytes)) return fail("truncated operand");
@@ -80,7 +83,7 @@ int main(int argc, char** argv) {
     for (int p = 0; p < JD_MAX_PEERS; ++p) d.out[p] = p < (int)nout ? dests[p] : nullptr;
     d.abort_word = nullptr;
     d.status = nullptr;
-    const int rc = jdb::run_pass_host(d);
+    const int rc = mode == 1 ? jdb::run_copy_fast_host(d) : jdb::run_pass_host(d);
     if (rc != 0) {
       std::fprintf(stderr, "host_selftest: case %llu returned %d (%s)\n", (unsigned long long)c, rc,
                    jdb::last_error_message());

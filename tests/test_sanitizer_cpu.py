@@ -21,7 +21,7 @@ from jaxdecomp_b200.parallel.mesh import pencil_type_from_pdims
 pytestmark = pytest.mark.skipif(not native.available() or native.sanitizer_compiler() is None,
                                 reason="needs the native core and a C++ compiler with the sanitizer run-times")
 
-MAGIC = 0x31464C455342444A
+MAGIC = 0x32464C455342444A
 
 
 def _cases(nat):
@@ -42,7 +42,7 @@ def _cases(nat):
             d = passes.fill_desc(nat, sp, eb, inverse, 0.5, batch, remote=sp.npeers > 1, device_tables=False)
             d.use_bulk = 0
             x = torch.randn((batch,) + tuple(sp.in_shape), dtype=dtype, generator=torch.Generator().manual_seed(len(out)))
-            out.append((d, x.contiguous(), [sp.numel * batch] * sp.npeers))
+            out.append((d, x.contiguous(), [sp.numel * batch] * sp.npeers, 0))
     # the six transposes as copy passes on float32 (4-byte elements)
     for kind in plan.TRANSPOSE_KINDS:
         specs, _ = passes.compile_passes(plan.transpose_steps(kind, True), (8, 12, 16), (2, 2), (0, 0))
@@ -50,7 +50,17 @@ def _cases(nat):
             d = passes.fill_desc(nat, sp, 4, False, 1.0, 1, remote=sp.npeers > 1, device_tables=False)
             d.use_bulk = 0
             x = torch.randn(tuple(sp.in_shape), dtype=torch.float32, generator=torch.Generator().manual_seed(99))
-            out.append((d, x.contiguous(), [sp.numel] * sp.npeers))
+            out.append((d, x.contiguous(), [sp.numel] * sp.npeers, 0))
+    # rotating copy passes in the host restatement of the 64 x 64-tile kernels, local and over two peers
+    for pdims, lshape, eb, dtype in (((1, 1), (64, 128, 64), 8, torch.complex64), ((1, 2), (64, 64, 128), 8, torch.float64),
+                                     ((2, 2), (32, 32, 64), 16, torch.complex128)):
+        for kind in ("x_y", "y_x"):
+            specs, _ = passes.compile_passes(plan.transpose_steps(kind, True), lshape, pdims, (0, 0))
+            sp = specs[0]
+            d = passes.fill_desc(nat, sp, eb, False, 1.0, 1, remote=sp.npeers > 1, device_tables=False)
+            d.use_bulk = 0
+            x = torch.randn(tuple(sp.in_shape), dtype=dtype, generator=torch.Generator().manual_seed(7))
+            out.append((d, x.contiguous(), [sp.numel] * sp.npeers, 1))
     # one chunk of a pipelined local pass
     specs, _ = passes.compile_passes(plan.fft_steps(pencil_type_from_pdims((1, 2)), False, True, native=True),
                                      (64, 32, 64), (1, 2), (0, 0))
@@ -59,7 +69,7 @@ def _cases(nat):
     d.use_bulk = 0
     half = sp.ext[2] // 2
     x = torch.randn(tuple(sp.in_shape), dtype=torch.complex64, generator=torch.Generator().manual_seed(5))
-    out.append((d.restricted(3, half, half), x.contiguous(), [sp.numel]))
+    out.append((d.restricted(3, half, half), x.contiguous(), [sp.numel], 0))
     return out
 
 
@@ -69,17 +79,19 @@ def test_host_passes_are_clean_under_asan_and_ubsan(tmp_path):
     cases = _cases(nat)
     want = []
     blob = [struct.pack("<QQQ", MAGIC, len(cases[0][0].raw_bytes()), len(cases))]
-    for d, x, out_elems in cases:
+    for d, x, out_elems, mode in cases:
         eb = d.elem_bytes
         raw = bytes(x.view(torch.uint8).reshape(-1).numpy()) if x.numel() else b""
-        blob += [d.raw_bytes(), struct.pack("<Q", len(raw)), raw, struct.pack("<Q", len(out_elems))]
+        blob += [d.raw_bytes(), struct.pack("<Q", mode), struct.pack("<Q", len(raw)), raw, struct.pack("<Q", len(out_elems))]
         blob += [struct.pack("<Q", n * eb) for n in out_elems]
         # the regular build on the same descriptor
         outs = [torch.zeros(n * eb, dtype=torch.uint8) for n in out_elems]
         d.in_ptr = x.data_ptr()
         for p, o in enumerate(outs):
             d.set_out(p, o.data_ptr())
-        nat.run_pass_host(d)
+        if mode == 1:
+            assert nat.copy_fast_eligible(d)
+        nat.run_pass_host(d)          # the general pass is the oracle for the restated kernels too
         want += outs
     (tmp_path / "cases.bin").write_bytes(b"".join(blob))
     r = subprocess.run([str(exe), str(tmp_path / "cases.bin"), str(tmp_path / "results.bin")], capture_output=True,
@@ -110,7 +122,7 @@ def test_sanitizer_build_catches_a_descriptor_that_overruns_its_destination(tmp_
     x = torch.randn(tuple(sp.in_shape), dtype=torch.complex64, generator=torch.Generator().manual_seed(1))
     raw = bytes(x.view(torch.uint8).reshape(-1).numpy())
     short = sp.numel * 8 // 2                       # half of what the pass writes; out_limit still says "all"
-    blob = [struct.pack("<QQQ", MAGIC, len(d.raw_bytes()), 1), d.raw_bytes(), struct.pack("<Q", len(raw)), raw,
+    blob = [struct.pack("<QQQ", MAGIC, len(d.raw_bytes()), 1), d.raw_bytes(), struct.pack("<Q", 0), struct.pack("<Q", len(raw)), raw,
             struct.pack("<Q", 1), struct.pack("<Q", short)]
     (tmp_path / "bad.bin").write_bytes(b"".join(blob))
     r = subprocess.run([str(exe), str(tmp_path / "bad.bin"), str(tmp_path / "out.bin")], capture_output=True, text=True,
