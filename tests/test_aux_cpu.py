@@ -145,6 +145,38 @@ def test_autotuned_config_chooses_among_transports(monkeypatch):
     assert jd.config.transpose_comm_backend == before
 
 
+def test_benchmark_report_tables(tmp_path, capsys):
+    """benchmarks/report.py: JSON lines of bench.py and bench_ops.py -> per-op table and strong-scaling efficiency."""
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("report", os.path.join(os.path.dirname(__file__), "..", "benchmarks", "report.py"))
+    report = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(report)
+    lines = [
+        {"metric": "m", "value": 1.0, "unit": "GFLOP/s", "n_gpus": 1, "ms_per_step": 20.0, "dtype": "complex64 (fp32)", "impl": "ours",
+         "config": {"pdims": [1, 1], "global_shape": [1024, 1024, 1024]}, "e2e": {"ms_per_step": 200.0}},
+        {"metric": "m", "value": 4.0, "unit": "GFLOP/s", "n_gpus": 4, "ms_per_step": 8.0, "dtype": "complex64 (fp32)", "impl": "ours",
+         "config": {"pdims": [1, 4], "global_shape": [1024, 1024, 1024]}},
+        {"metric": "m", "value": 4.5, "unit": "GFLOP/s", "n_gpus": 4, "ms_per_step": 7.0, "dtype": "complex64 (fp32)", "impl": "ours",
+         "config": {"pdims": [2, 2], "global_shape": [1024, 1024, 1024]}},
+        {"op": "halo_exchange", "backend": "b200", "halo": 16, "ms": 0.25, "egress_gbs": 500.0, "n_gpus": 4, "pdims": [2, 2],
+         "global_shape": [1024, 1024, 1024], "dtype": "c64"},
+        {"impl": "reference", "unavailable": "no jax"},
+    ]
+    f = tmp_path / "r.jsonl"
+    f.write_text("some log line\n" + "\n".join(json.dumps(d) for d in lines) + "\n")
+    recs = report.read_records([str(f)])
+    assert len(recs) == 4
+    rows = report.scaling_rows(recs)
+    assert [r["n_gpus"] for r in rows] == [1, 4]                      # the halo op has a single GPU count: left out
+    assert rows[1]["pdims"] == "2x2" and rows[1]["ms"] == 7.0         # the faster grid at 4 GPUs
+    assert rows[1]["efficiency"] == pytest.approx(20.0 / (4 * 7.0)) and rows[1]["speedup"] == pytest.approx(20.0 / 7.0)
+    assert report.main([str(f)]) == 0
+    out = capsys.readouterr().out
+    assert "## Strong scaling" in out and "halo_exchange h=16" in out and "0.714" in out
+    assert report.main([str(f), "--csv"]) == 0 and "op,backend,shape" in capsys.readouterr().out
+
+
 def test_init_finalize_are_idempotent():
     jd.init()
     jd.finalize()
