@@ -262,6 +262,9 @@ def so_path() -> Path:
 
 
 if __name__ == "__main__":
-    p = build(verbose=True, force="--force" in sys.argv, ptxas_info="--ptxas" in sys.argv,
-              bounds=True if "--bounds" in sys.argv else None)
-    print(p)
+    # python -m jaxdecomp_b200.native [--force] [--ptxas] [--bounds] | --selftest
+    if "--selftest" in sys.argv:
+        print(build_host_selftest(force="--force" in sys.argv))
+    else:
+        print(build(verbose=True, force="--force" in sys.argv, ptxas_info="--ptxas" in sys.argv,
+                    bounds=True if "--bounds" in sys.argv else None))
