@@ -183,3 +183,45 @@ def test_gradcheck_and_double_backward_on_a_single_rank():
     with jd.single_rank_mesh():
         assert torch.autograd.gradcheck(lambda v: jd.halo_exchange(v, (1, 1), (True, True)), (x,))
         assert torch.autograd.gradcheck(lambda v: jd.halo_accumulate(v, (1, 1), (True, True)), (x,))
+
+
+def _halo_fit_worker(rank, world, pdims):
+    # the reference's halo gradient test (tests/test_halo.py:313-398): a least-squares loss through
+    # pad + halo_exchange has zero gradient at the observation; away from it the gradient is
+    # 2 L^T (L x - obs), which is checked against a directional finite difference over all ranks
+    mesh = jd.make_mesh(pdims, ("z", "y"))
+    h = (2 if pdims[0] > 1 else 0, 2 if pdims[1] > 1 else 0)
+    x0 = torch.randn((16 // pdims[0], 16 // pdims[1], 4), dtype=torch.float64, generator=torch.Generator().manual_seed(90 + rank))
+
+    def forward(v):
+        return jd.halo_exchange(jd.pad_halo(jd.ShardedTensor(v, mesh), h), h, (True, True)).local
+
+    obs = forward(x0).detach()
+
+    def loss(v):
+        return ((forward(v) - obs) ** 2).sum()      # this rank's part; the global loss is the sum over ranks
+
+    def global_loss(v):
+        t = loss(v).detach().clone()
+        torch.distributed.all_reduce(t)
+        return float(t)
+
+    x = x0.clone().requires_grad_(True)
+    loss(x).backward()
+    assert torch.equal(x.grad, torch.zeros_like(x0))
+    x = (2 * x0).clone().requires_grad_(True)
+    loss(x).backward()
+    g = x.grad.clone()
+    direction = torch.randn(x0.shape, dtype=torch.float64, generator=torch.Generator().manual_seed(190 + rank))
+    eps = 1e-6
+    fd = (global_loss(2 * x0 + eps * direction) - global_loss(2 * x0 - eps * direction)) / (2 * eps)
+    an = (g * direction).sum()
+    torch.distributed.all_reduce(an)
+    assert abs(float(an) - fd) <= 1e-6 * max(1.0, abs(fd)), (float(an), fd)
+    # every interior cell also appears in some neighbour's halo: the gradient is larger than the local term alone
+    assert (g.abs() >= (2 * x0).abs() - 1e-12).all()
+
+
+def test_least_squares_gradient_through_pad_and_halo_exchange():
+    for pdims in ((2, 4), (1, 8), (4, 2)):
+        run_ranks(_halo_fit_worker, 8, pdims)
